@@ -8,6 +8,15 @@
 // tm_glu_routed: gu [T, E, 2, F] (per expert: gate rows, then up rows) -> act [T, E, F] = silu(gate) * up * weight[t, e],
 // exactly zero for experts the token did not choose (their products are never looked at), so that ONE matrix product
 // of act with the experts' down matrices laid side by side along K gives the weighted sum of the chosen experts.
+//
+// tm_moe_choose: a router that scores every output with a softmax over ALL of them, s = softmax(z), chooses by
+// s + correction (a learned vector that does not enter the weights), may restrict the choice to the best `keep` of
+// `groups` equal groups of neighbouring outputs (a group's score: its largest choice score; outputs of other groups
+// count as minus infinity), and weighs the `top` chosen by their s divided by the sum of the chosen s (+ 1e-20). The last
+// `identity` outputs have no expert behind them: their result is the token's input itself; their summed weight is
+// written per token beside the dense row of weights.
+//
+// tm_act_routed: up [T, E, F] -> act [T, E, F] = act(up) * weight[t, e] (act: the square of relu), zero where not chosen.
 #include "common.cuh"
 
 namespace tmk {
@@ -70,6 +79,139 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
       dense_w[(size_t)t * E + top_idx[(size_t)t * top + k]] = wv;
     }
   }
+}
+
+// One warp per token over its n = experts + identity logits (32-bit). Ties go to the lowest index, in groups and outputs.
+__global__ void __launch_bounds__(128) moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
+                                                         int* __restrict__ top_idx, float* __restrict__ top_w,
+                                                         float* __restrict__ dense_w, float* __restrict__ identity_w, int T_,
+                                                         int n, int top, int groups, int keep, int identity) {
+  extern __shared__ float sm[];               // per warp: n scores, n choice scores, `groups` group scores
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T_) return;
+  float* score = sm + (size_t)warp * (2 * n + groups);
+  float* choice = score + n;
+  float* gscore = choice + n;
+  float mx = -INFINITY;
+  for (int e = lane; e < n; e += 32) {
+    const float v = logits[(size_t)t * n + e];
+    score[e] = v;
+    mx = fmaxf(mx, v);
+    dense_w[(size_t)t * n + e] = 0.f;
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < n; e += 32) {
+    const float ex = expf(score[e] - mx);
+    score[e] = ex;
+    sum += ex;
+  }
+  sum = warp_sum(sum);
+  for (int e = lane; e < n; e += 32) {
+    score[e] = score[e] / sum;
+    choice[e] = score[e] + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int per = n / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float best = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, choice[e]);
+      gscore[g] = best;
+    }
+    __syncwarp();
+    // `keep` rounds of arg-max over the groups; a kept group is marked by +inf, the others are closed afterwards
+    for (int k = 0; k < keep; ++k) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = gscore[g];
+        if (v != INFINITY && (v > bv || (v == bv && g < bi) || bi == 0x7fffffff)) { bv = v; bi = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+      }
+      if (lane == 0 && bi != 0x7fffffff) gscore[bi] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < n; e += 32)
+      if (gscore[e / per] != INFINITY) choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  // `top` rounds of arg-max over the choice scores; a chosen output is marked by NaN in the scratch copy
+  float denom = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < n; e += 32) {
+      const float v = choice[e];
+      if (v != v) continue;
+      if (bi == 0x7fffffff || v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    }
+    const float sv = score[bi];
+    denom += sv;
+    if (lane == 0) {
+      top_idx[(size_t)t * top + k] = bi;
+      top_w[(size_t)t * top + k] = sv;
+      choice[bi] = __int_as_float(0x7fc00000);
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    float idw = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int e = top_idx[(size_t)t * top + k];
+      const float wv = top_w[(size_t)t * top + k] / (denom + 1e-20f);
+      top_w[(size_t)t * top + k] = wv;
+      dense_w[(size_t)t * n + e] = wv;
+      if (e >= n - identity) idw += wv;
+    }
+    if (identity_w) identity_w[t] = idw;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) act_routed_kernel(const T* __restrict__ up, const float* __restrict__ dense_w,
+                                                         int dense_stride, T* __restrict__ act, int E, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, e = blockIdx.y;
+  const float wv = dense_w[(size_t)t * dense_stride + e];
+  const T* u = up + ((size_t)t * E + e) * F;
+  T* o = act + ((size_t)t * E + e) * F;
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    float v = 0.f;
+    if (wv != 0.f) {
+      const float r = fmaxf(to_float(u[i]), 0.f);
+      v = r * r * wv;
+    }
+    o[i] = from_float<T>(v);
+  }
+}
+
+// out[t] += w[t] * x[t], row by row (the share of router outputs whose result is the input itself).
+template <typename T>
+__global__ void __launch_bounds__(256) add_scaled_rows_kernel(T* __restrict__ out, const T* __restrict__ x,
+                                                              const float* __restrict__ w, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float wv = w[t];
+  if (wv == 0.f) return;
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[(size_t)t * H + i] = from_float<T>(fmaf(wv, to_float(x[(size_t)t * H + i]), to_float(out[(size_t)t * H + i])));
 }
 
 template <typename T>
@@ -171,6 +313,46 @@ extern "C" int tm_glu_routed(int dtype, const void* gu, const float* dense_w, vo
   if (dtype == TM_DTYPE_BF16)
     return tmk::launch_pdl(tmk::glu_routed_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)gu,
                            dense_w, (__nv_bfloat16*)act, E, F);
+  return TM_ERR_BAD_DTYPE;
+}
+
+// logits [T, n] float, n = experts + identity; correction [n] float or null; top_idx [T, top] int; top_w [T, top],
+// dense_w [T, n] float; identity_w [T] float or null.
+extern "C" int tm_moe_choose(const float* logits, const float* correction, int* top_idx, float* top_w, float* dense_w,
+                             float* identity_w, int T, int n, int top, int groups, int keep, int identity, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (top < 1 || top > n || n > 2048 || groups < 1 || n % groups || keep < 1 || keep > groups || identity < 0 || identity > n ||
+      top > keep * (n / groups))
+    return TM_ERR_UNSUPPORTED_SHAPE;
+  const int warps = 4;
+  return tmk::launch_pdl(tmk::moe_choose_kernel, dim3((T + warps - 1) / warps), dim3(warps * 32),
+                         (size_t)warps * (2 * n + groups) * sizeof(float), stream, logits, correction, top_idx, top_w, dense_w,
+                         identity_w, T, n, top, groups, keep, identity);
+}
+
+// up [T, E, F], act [T, E, F] dtype; dense_w float, token t's weights at dense_w + t * dense_stride.
+extern "C" int tm_act_routed(int dtype, const void* up, const float* dense_w, int dense_stride, void* act, int T, int E, int F,
+                             cudaStream_t stream) {
+  if (T <= 0 || E <= 0) return 0;
+  if (E > 65535) return TM_ERR_UNSUPPORTED_SHAPE;
+  const dim3 grid(T, E);
+  if (dtype == TM_DTYPE_F32)
+    return tmk::launch_pdl(tmk::act_routed_kernel<float>, grid, dim3(128), 0, stream, (const float*)up, dense_w, dense_stride,
+                           (float*)act, E, F);
+  if (dtype == TM_DTYPE_BF16)
+    return tmk::launch_pdl(tmk::act_routed_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)up, dense_w,
+                           dense_stride, (__nv_bfloat16*)act, E, F);
+  return TM_ERR_BAD_DTYPE;
+}
+
+// out, x [T, H] dtype; w [T] float.
+extern "C" int tm_add_scaled_rows(int dtype, void* out, const void* x, const float* w, int T, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (dtype == TM_DTYPE_F32)
+    return tmk::launch_pdl(tmk::add_scaled_rows_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)out, (const float*)x, w, H);
+  if (dtype == TM_DTYPE_BF16)
+    return tmk::launch_pdl(tmk::add_scaled_rows_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out,
+                           (const __nv_bfloat16*)x, w, H);
   return TM_ERR_BAD_DTYPE;
 }
 

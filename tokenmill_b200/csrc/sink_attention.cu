@@ -1,14 +1,16 @@
 // Grouped-query attention over a paged cache of [keys | values] rows, with the options a windowed design may combine:
 // key and value heads of different sizes, a norm over the whole query / key projection, rotation of the first
 // `rot_dims` dimensions of each head, a tanh cap on the scores, a sliding window that keeps the sequence's first
-// tokens visible, a softmax with one more term of score 0 (a sink without a value), and a per-head output gate.
-// Each option is a parameter and may be switched off.
+// tokens visible, a softmax with one more term of score 0 (a sink without a value), an output gate per head or per
+// output number, and a query temperature that grows with the position. Each option is a parameter and may be switched off.
 //
 // tm_qk_norm_rope_write, one block per token, reads the token's row of a 32-bit projection
-//   [q (H d) | k (G d) | v (G dv) | g (H)]        (g only with gate_out)
+//   [q (H d) | k (G d) | v (G dv) | g (gate_cols)]        (g only with gate_out; k and v only with has_kv: a layer that
+//                                                          reads another layer's keys and values has none)
 // and writes: q, RMS-normed over all its H d numbers at once (weight wq; skipped when wq is null) and rotated, in the
 // activation dtype; [k | v] to the token's cache row, k normed over its G d numbers (wk) and rotated; sigmoid(g) in
-// 32-bit. The rotation pairs dimension i with i + rot_dims / 2 inside each head; angles come from 32-bit tables
+// 32-bit. With temp_every > 0 the query is multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) at position
+// p (32-bit). The rotation pairs dimension i with i + rot_dims / 2 inside each head; angles come from 32-bit tables
 // [positions, rot_dims / 2].
 //
 // tm_sink_attention: 32-bit arithmetic on CUDA cores for both dtypes. A tile is 32 consecutive (token, head in group)
@@ -27,15 +29,17 @@ __global__ void __launch_bounds__(256) qk_norm_rope_write_kernel(
     const float* __restrict__ proj, long long ld, int H, int G, int d, int dv, int rot_dims, const float* __restrict__ wq,
     const float* __restrict__ wk, float eps, const int* __restrict__ positions, const float* __restrict__ cos_t,
     const float* __restrict__ sin_t, int n_positions, const int* __restrict__ slot_map, T* __restrict__ q_out,
-    T* __restrict__ cache, float* __restrict__ gate_out, int* __restrict__ error) {
+    T* __restrict__ cache, float* __restrict__ gate_out, int gate_cols, int has_kv, float temp_coef, int temp_every,
+    int* __restrict__ error) {
   extern __shared__ __align__(16) float staged[];    // the token's q and k columns: read once, used three times
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const float* row = proj + (size_t)t * ld;
-  const int nq = H * d, nk = G * d, nv = G * dv;
+  const int nq = H * d, nk = has_kv ? G * d : 0, nv = has_kv ? G * dv : 0;
   const int pos = positions[t];
+  const float temp = temp_every > 0 ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
   const int half = rot_dims >> 1;
   if (rot_dims > 0 && (pos < 0 || pos >= n_positions)) {   // never read outside the tables: report instead
     if (threadIdx.x == 0) atomicExch(error, 31);
@@ -73,14 +77,14 @@ __global__ void __launch_bounds__(256) qk_norm_rope_write_kernel(
       const float o = src[i - half] * r * (w ? w[i - half] : 1.f);
       v = __fadd_rn(__fmul_rn(v, ct[e - half]), __fmul_rn(o, st[e - half]));
     }
-    if (is_q) q_out[(size_t)t * nq + i] = from_float<T>(v);
+    if (is_q) q_out[(size_t)t * nq + i] = from_float<T>(v * temp);
     else crow[i] = from_float<T>(v);
   }
   if (crow)
     for (int i = threadIdx.x; i < nv; i += blockDim.x) crow[nk + i] = from_float<T>(row[nq + nk + i]);
   if (gate_out)
-    for (int i = threadIdx.x; i < H; i += blockDim.x)
-      gate_out[(size_t)t * H + i] = 1.0f / (1.0f + expf(-row[nq + nk + nv + i]));
+    for (int i = threadIdx.x; i < gate_cols; i += blockDim.x)
+      gate_out[(size_t)t * gate_cols + i] = 1.0f / (1.0f + expf(-row[nq + nk + nv + i]));
 }
 
 constexpr int kSinkWarps = 8;
@@ -93,7 +97,7 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attention_kernel(
     const T* __restrict__ q, const T* __restrict__ cache, int row_width, int v_off, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_before, const int* __restrict__ tile_seq,
     const int* __restrict__ tile_row0, const float* __restrict__ gate, T* __restrict__ out, int H, int G, int d, int dv,
-    int page_size, float scale, float softcap, int window, int keep_first, int sink) {
+    int page_size, float scale, float softcap, int window, int keep_first, int sink, int gate_wide) {
   extern __shared__ __align__(16) float smem[];
   const int KS = d + 1;                           // padded key row: lanes read different rows, same column
   float* qs = smem;                               // [32][d]
@@ -215,12 +219,13 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attention_kernel(
     if (row >= n_rows) continue;
     const int tok = q_start + row / Gq, head = kvh * Gq + row % Gq;
     float f = l[i] > 0.f ? 1.0f / l[i] : 0.f;
-    if (gate) f *= gate[(size_t)tok * H + head];
+    if (gate && !gate_wide) f *= gate[(size_t)tok * H + head];
     T* o = out + ((size_t)tok * H + head) * dv;
+    const float* gw = (gate && gate_wide) ? gate + ((size_t)tok * H + head) * dv : nullptr;
 #pragma unroll
     for (int dd = 0; dd < NDV; ++dd) {
       const int e = lane + 32 * dd;
-      if (e < dv) o[e] = from_float<T>(acc[i][dd] * f);
+      if (e < dv) o[e] = from_float<T>(acc[i][dd] * f * (gw ? gw[e] : 1.0f));
     }
   }
 }
@@ -229,7 +234,7 @@ template <typename T>
 int launch_sink_attention(const void* q, const void* cache, int row_width, int v_off, const int* block_table, int bt_stride,
                           const int* cu_q, const int* kv_before, const int* tile_seq, const int* tile_row0, int n_tiles,
                           const float* gate, void* out, int H, int G, int d, int dv, int page_size, float scale,
-                          float softcap, int window, int keep_first, int sink, cudaStream_t stream) {
+                          float softcap, int window, int keep_first, int sink, int gate_wide, cudaStream_t stream) {
   const size_t smem = ((size_t)kSinkTileRows * d + (size_t)kSinkKeyTile * (d + 1) + (size_t)kSinkKeyTile * dv) * sizeof(float);
   if (smem > 220 * 1024 || dv > 256 || H % G) return TM_ERR_UNSUPPORTED_SHAPE;
   const int nd = (dv + 31) / 32;
@@ -242,7 +247,7 @@ int launch_sink_attention(const void* q, const void* cache, int row_width, int v
     }                                                                                                             \
     return launch_pdl(kern, dim3(n_tiles, G), dim3(kSinkWarps * 32), smem, stream, (const T*)q, (const T*)cache,  \
                       row_width, v_off, block_table, bt_stride, cu_q, kv_before, tile_seq, tile_row0, gate, (T*)out, H, G, \
-                      d, dv, page_size, scale, softcap, window, keep_first, sink);                                \
+                      d, dv, page_size, scale, softcap, window, keep_first, sink, gate_wide);                     \
   }
   switch (nd) {
     TM_SINK_CASE(1) TM_SINK_CASE(2) TM_SINK_CASE(3) TM_SINK_CASE(4) TM_SINK_CASE(5) TM_SINK_CASE(6) TM_SINK_CASE(7)
@@ -255,13 +260,16 @@ int launch_sink_attention(const void* q, const void* cache, int row_width, int v
 }  // namespace tmk
 
 // proj: float, token t's row at proj + t * ld; wq [H d], wk [G d] float or null; cos/sin [n_positions, rot_dims / 2] float;
-// slot_map [T] or null (negative: not cached); q_out [T, H d]; cache [slots, G d + G dv]; gate_out [T, H] float or null.
+// slot_map [T] or null (negative: not cached); q_out [T, H d]; cache [slots, G d + G dv]; gate_out [T, gate_cols] float or
+// null; has_kv 0: the row is [q | g] only; temp_every > 0: the query temperature.
 extern "C" int tm_qk_norm_rope_write(int dtype, const float* proj, long long ld, int H, int G, int d, int dv, int rot_dims,
                                      const float* wq, const float* wk, float eps, const int* positions, const float* cos_t,
                                      const float* sin_t, int n_positions, const int* slot_map, void* q_out, void* cache,
-                                     float* gate_out, int T_rows, int* error, cudaStream_t stream) {
+                                     float* gate_out, int gate_cols, int has_kv, float temp_coef, int temp_every, int T_rows,
+                                     int* error, cudaStream_t stream) {
   if (T_rows <= 0) return 0;
-  if (rot_dims % 2 || rot_dims > d || rot_dims < 0 || H <= 0 || G <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (rot_dims % 2 || rot_dims > d || rot_dims < 0 || H <= 0 || G <= 0 || temp_every < 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (!has_kv && (cache || wk)) return TM_ERR_UNSUPPORTED_SHAPE;
   const size_t smem = (size_t)(H + G) * d * sizeof(float);
   if (smem > 200 * 1024) return TM_ERR_UNSUPPORTED_SHAPE;
   if (smem > 40 * 1024) {
@@ -273,29 +281,30 @@ extern "C" int tm_qk_norm_rope_write(int dtype, const float* proj, long long ld,
   if (dtype == TM_DTYPE_F32)
     return tmk::launch_pdl(tmk::qk_norm_rope_write_kernel<float>, dim3(T_rows), dim3(256), smem, stream, proj, ld, H, G, d, dv,
                            rot_dims, wq, wk, eps, positions, cos_t, sin_t, n_positions, slot_map, (float*)q_out,
-                           (float*)cache, gate_out, error);
+                           (float*)cache, gate_out, gate_cols, has_kv, temp_coef, temp_every, error);
   if (dtype == TM_DTYPE_BF16)
     return tmk::launch_pdl(tmk::qk_norm_rope_write_kernel<__nv_bfloat16>, dim3(T_rows), dim3(256), smem, stream, proj, ld, H, G,
                            d, dv, rot_dims, wq, wk, eps, positions, cos_t, sin_t, n_positions, slot_map,
-                           (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, gate_out, error);
+                           (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, gate_out, gate_cols, has_kv, temp_coef, temp_every,
+                           error);
   return TM_ERR_BAD_DTYPE;
 }
 
 // q [T, H, d]; cache [pages, page_size, row_width] with head g's key at g * d and its value at v_off + g * dv; tiles of 32
-// (token, head in group) rows; gate [T, H] float or null; out [T, H, dv].
+// (token, head in group) rows; gate [T, H] float (gate_wide: [T, H, dv]) or null; out [T, H, dv].
 extern "C" int tm_sink_attention(int dtype, const void* q, const void* cache, int row_width, int v_off,
                                  const int* block_table, int bt_stride, const int* cu_q, const int* kv_before,
                                  const int* tile_seq, const int* tile_row0, int n_tiles, const float* gate, void* out, int H,
                                  int G, int d, int dv, int page_size, float scale, float softcap, int window, int keep_first,
-                                 int sink, cudaStream_t stream) {
+                                 int sink, int gate_wide, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (dtype == TM_DTYPE_F32)
     return tmk::launch_sink_attention<float>(q, cache, row_width, v_off, block_table, bt_stride, cu_q, kv_before, tile_seq,
                                              tile_row0, n_tiles, gate, out, H, G, d, dv, page_size, scale, softcap, window,
-                                             keep_first, sink, stream);
+                                             keep_first, sink, gate_wide, stream);
   if (dtype == TM_DTYPE_BF16)
     return tmk::launch_sink_attention<__nv_bfloat16>(q, cache, row_width, v_off, block_table, bt_stride, cu_q, kv_before,
                                                      tile_seq, tile_row0, n_tiles, gate, out, H, G, d, dv, page_size, scale,
-                                                     softcap, window, keep_first, sink, stream);
+                                                     softcap, window, keep_first, sink, gate_wide, stream);
   return TM_ERR_BAD_DTYPE;
 }

@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_before,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0, const float* __restrict__ gate,
     __nv_bfloat16* __restrict__ out, int H, int G, int page_size, float scale, float softcap, int window, int keep_first,
-    int sink, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    int sink, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int gate_wide) {
   constexpr int THREADS = kSmWarps * 32;
   constexpr int CHK = DK / 8, CHV = DV / 8;     // 16-byte chunks per key / value row
   constexpr int TPR = THREADS / kSmBN;          // threads that share one key row when loading (2)
@@ -269,11 +269,15 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
   for (int hh = 0; hh < 2; ++hh) {
     if (p_row[hh] < 0) continue;
     float f = l_run[hh] > 0.f ? 1.0f / l_run[hh] : 0.f;
-    if (gate) f *= gate[o_row[hh]];
+    if (gate && !gate_wide) f *= gate[o_row[hh]];
     __nv_bfloat16* dst = out + o_row[hh] * DV;
+    const float* gw = (gate && gate_wide) ? gate + o_row[hh] * DV : nullptr;
 #pragma unroll
-    for (int t = 0; t < NT; ++t)
-      *reinterpret_cast<uint32_t*>(dst + t * 8 + cpair) = pack_bf16(o[t][2 * hh] * f, o[t][2 * hh + 1] * f);
+    for (int t = 0; t < NT; ++t) {
+      float g0 = 1.f, g1 = 1.f;
+      if (gw) { g0 = gw[t * 8 + cpair]; g1 = gw[t * 8 + cpair + 1]; }
+      *reinterpret_cast<uint32_t*>(dst + t * 8 + cpair) = pack_bf16(o[t][2 * hh] * f * g0, o[t][2 * hh + 1] * f * g1);
+    }
   }
 }
 
@@ -282,7 +286,7 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
 __global__ void __launch_bounds__(256) sink_attention_combine_kernel(
     const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ cu_q,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0, const float* __restrict__ gate,
-    __nv_bfloat16* __restrict__ out, int H, int G, int dv, int n_splits) {
+    __nv_bfloat16* __restrict__ out, int H, int G, int dv, int n_splits, int gate_wide) {
   pdl_launch_dependents();
   pdl_wait();
   const int s = tile_seq[blockIdx.x], row0 = tile_row0[blockIdx.x], kvh = blockIdx.y;
@@ -302,14 +306,15 @@ __global__ void __launch_bounds__(256) sink_attention_combine_kernel(
     const int row = row0 + r;
     const size_t o_row = (size_t)(q_start + row / Gq) * H + kvh * Gq + row % Gq;
     float f = L > 0.f ? 1.0f / L : 0.f;
-    if (gate) f *= gate[o_row];
+    if (gate && !gate_wide) f *= gate[o_row];
+    const float* gw = (gate && gate_wide) ? gate + o_row * dv : nullptr;
     for (int e = lane; e < dv; e += 32) {
       float acc = 0.f;
       for (int z = 0; z < n_splits; ++z) {
         const float mz = part_ml[((base + z) * kSmBM + r) * 2];
         if (mz != -INFINITY) acc += part_o[((base + z) * kSmBM + r) * dv + e] * exp2f(mz - M);
       }
-      out[o_row * dv + e] = __float2bfloat16_rn(acc * f);
+      out[o_row * dv + e] = __float2bfloat16_rn(acc * f * (gw ? gw[e] : 1.0f));
     }
   }
 }
@@ -319,7 +324,7 @@ int launch_sink_attention_mma(const void* q, const void* cache, int row_width, i
                               int bt_stride, const int* cu_q, const int* kv_before, const int* tile_seq,
                               const int* tile_row0, int n_tiles, const float* gate, void* out, int H, int G, int page_size,
                               float scale, float softcap, int window, int keep_first, int sink, int n_splits, float* part_o,
-                              float* part_ml, cudaStream_t stream) {
+                              float* part_ml, int gate_wide, cudaStream_t stream) {
   constexpr int STAGES = (DK + DV) >= 256 ? 2 : 3;
   const int smem = STAGES * kSmBN * (DK + DV) * 2;
   auto kern = sink_attention_mma_kernel<DK, DV, STAGES>;
@@ -330,17 +335,17 @@ int launch_sink_attention_mma(const void* q, const void* cache, int row_width, i
   const int st = launch_pdl(kern, dim3(n_tiles, G, n_splits), dim3(kSmWarps * 32), (size_t)smem, stream,
                             (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, row_width, v_off, block_table, bt_stride, cu_q,
                             kv_before, tile_seq, tile_row0, gate, (__nv_bfloat16*)out, H, G, page_size, scale, softcap, window,
-                            keep_first, sink, n_splits, part_o, part_ml);
+                            keep_first, sink, n_splits, part_o, part_ml, gate_wide);
   if (st != 0 || n_splits == 1) return st;
   return launch_pdl(sink_attention_combine_kernel, dim3(n_tiles, G), dim3(256), 0, stream, (const float*)part_o,
-                    (const float*)part_ml, cu_q, tile_seq, tile_row0, gate, (__nv_bfloat16*)out, H, G, DV, n_splits);
+                    (const float*)part_ml, cu_q, tile_seq, tile_row0, gate, (__nv_bfloat16*)out, H, G, DV, n_splits, gate_wide);
 }
 
 }  // namespace tmk
 
 // q [T, H, d] bfloat16; cache [pages, page_size, row_width] bfloat16 with head g's key at g * d and its value at
 // v_off + g * dv (row_width and v_off multiples of 8); tiles of 64 (token, head in group) rows of one request; gate
-// [T, H] float or null; out [T, H, dv] bfloat16. d and dv each 32, 64 or 128; the scale positive. n_splits > 1: a
+// [T, H] float (gate_wide: [T, H, dv]) or null; out [T, H, dv] bfloat16. d and dv each 32, 64 or 128; the scale positive. n_splits > 1: a
 // tile's key blocks are dealt out over that many blocks, through part_o [n_tiles * G * n_splits, 64, dv] and part_ml
 // [n_tiles * G * n_splits, 64, 2] float, and merged by a second launch.
 extern "C" int tm_sink_attention_mma_bf16(const void* q, const void* cache, int row_width, int v_off,
@@ -348,7 +353,7 @@ extern "C" int tm_sink_attention_mma_bf16(const void* q, const void* cache, int 
                                           const int* tile_seq, const int* tile_row0, int n_tiles, const float* gate,
                                           void* out, int H, int G, int d, int dv, int page_size, float scale, float softcap,
                                           int window, int keep_first, int sink, int n_splits, float* part_o, float* part_ml,
-                                          cudaStream_t stream) {
+                                          int gate_wide, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (n_splits < 1 || (n_splits > 1 && (!part_o || !part_ml))) return TM_ERR_SCRATCH_TOO_SMALL;
   if (G <= 0 || H % G || page_size <= 0 || (row_width & 7) || (v_off & 7) || !(scale > 0.f)) return TM_ERR_UNSUPPORTED_SHAPE;
@@ -356,7 +361,7 @@ extern "C" int tm_sink_attention_mma_bf16(const void* q, const void* cache, int 
   if (d == DKK && dv == DVV)                                                                                          \
     return tmk::launch_sink_attention_mma<DKK, DVV>(q, cache, row_width, v_off, block_table, bt_stride, cu_q, kv_before, \
                                                     tile_seq, tile_row0, n_tiles, gate, out, H, G, page_size, scale, softcap, \
-                                                    window, keep_first, sink, n_splits, part_o, part_ml, stream);
+                                                    window, keep_first, sink, n_splits, part_o, part_ml, gate_wide, stream);
   TM_SM_CASE(32, 32) TM_SM_CASE(32, 64) TM_SM_CASE(32, 128) TM_SM_CASE(64, 32) TM_SM_CASE(64, 64) TM_SM_CASE(64, 128)
   TM_SM_CASE(128, 32) TM_SM_CASE(128, 64) TM_SM_CASE(128, 128)
 #undef TM_SM_CASE

@@ -87,10 +87,18 @@ _SIGNATURES: dict[str, list] = {
     "tm_glu": [_I, _I, _P, _P, _I, _I, _P],
     "tm_norm_pair_mean": [_I, _P, _P, _P, _P, _F, _P, _I, _I, _P],
     "tm_head_norm_gate": [_I, _P, _P, _P, _LL, _P, _F, _P, _I, _I, _I, _P],
-    "tm_qk_norm_rope_write": [_I, _P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P],
-    "tm_sink_attention": [_I, _P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P],
+    "tm_qk_norm_rope_write": [_I, _P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _F, _I, _I,
+                              _P, _P],
+    "tm_sink_attention": [_I, _P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _P],
     "tm_sink_attention_mma_bf16": [_P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I,
-                                   _P, _P, _P],
+                                   _P, _P, _I, _P],
+    "tm_moe_choose": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "tm_act_routed": [_I, _P, _P, _I, _P, _I, _I, _I, _P],
+    "tm_add_scaled_rows": [_I, _P, _P, _P, _I, _I, _P],
+    "tm_stream_norm": [_I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _P, _P, _P, _F, _P, _I, _P],
+    "tm_softcap": [_P, _LL, _F, _P],
+    "tm_selective_scan": [_I, _P, _I, _P, _LL, _I, _P, _LL, _I, _I, _P, _P, _P, _P, _P, _LL, _LL, _P, _P, _P, _I, _P],
+    "tm_decay_memory": [_P, _LL, _I, _I, _I, _I, _P, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _P],
     "tm_matrix_memory": [_P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P, _LL, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P,
                          _LL, _I, _P],
     "tm_matrix_memory_pass_states": [_P, _LL, _LL, _P, _P, _I, _I, _I, _I, _I, _P, _LL, _P],
@@ -99,24 +107,56 @@ _SIGNATURES: dict[str, list] = {
 }
 
 
-# Entry points of the "hybrid" and "gated" libraries; everything else is in "main". The 32-bit matrix product is in all
-# and is taken from whichever is loaded (a model that needs only one library builds only that one).
-_HYBRID = {"tm_add_norm_pair", "tm_token_shift", "tm_gated_group_norm", "tm_latent_prepare", "tm_latent_attention",
-           "tm_latent_attention_mma_bf16", "tm_conv_silu_state", "tm_ssm_scan", "tm_ssm_pass_states", "tm_relu2",
-           "tm_moe_topk", "tm_glu_routed", "tm_gemm_f32_nt_batched"}
-_GATED = {"tm_gated_add_rmsnorm", "tm_canon_conv", "tm_glu", "tm_norm_pair_mean", "tm_head_norm_gate",
-          "tm_qk_norm_rope_write", "tm_sink_attention", "tm_sink_attention_mma_bf16", "tm_matrix_memory", "tm_matrix_memory_pass_states"}
+# Entry points of the libraries beside "main", file by file; everything else is in "main". A file may be part of several
+# libraries (kernels/build.py); the 32-bit matrix product is in all.
+_BY_FILE = {
+    "norm_pair.cu": {"tm_add_norm_pair", "tm_token_shift", "tm_gated_group_norm"},
+    "latent_attention.cu": {"tm_latent_prepare", "tm_latent_attention"},
+    "latent_attention_mma_bf16.cu": {"tm_latent_attention_mma_bf16"},
+    "ssm_scan.cu": {"tm_conv_silu_state", "tm_ssm_scan", "tm_ssm_pass_states"},
+    "routed_ffn.cu": {"tm_relu2", "tm_moe_topk", "tm_glu_routed", "tm_gemm_f32_nt_batched", "tm_moe_choose", "tm_act_routed",
+                      "tm_add_scaled_rows"},
+    "gated_block.cu": {"tm_gated_add_rmsnorm", "tm_canon_conv", "tm_glu", "tm_norm_pair_mean", "tm_head_norm_gate"},
+    "sink_attention.cu": {"tm_qk_norm_rope_write", "tm_sink_attention"},
+    "sink_attention_mma_bf16.cu": {"tm_sink_attention_mma_bf16"},
+    "matrix_memory.cu": {"tm_matrix_memory", "tm_matrix_memory_pass_states"},
+    "stream_norm.cu": {"tm_stream_norm", "tm_softcap"},
+    "selective_scan.cu": {"tm_selective_scan"},
+    "decay_memory.cu": {"tm_decay_memory"},
+}
 _BOTH = {"tm_gemm_f32_nt"}            # in every library
+_GROUPS_OF: dict[str, list[str]] = {}     # entry point -> the libraries that hold it, in the order of kernels/build.py
+for _group, _files in _build._FILES.items():
+    for _file in _files:
+        for _name in _BY_FILE[_file]:
+            _GROUPS_OF.setdefault(_name, []).append(_group)
+_preferred: list[str] = []            # libraries a model has said it runs from (``prefer``), latest first
 
 
-def _home(name: str) -> str:
-    return "hybrid" if name in _HYBRID else "gated" if name in _GATED else "main"
+def prefer(group: str) -> None:
+    """Say that entry points which several libraries hold are to come from ``group`` when none of those is loaded yet
+    (a model whose kernels are all in one library then builds and loads that one only)."""
+    if group not in _build.GROUPS:
+        raise KernelError(f"unknown kernel library {group!r}")
+    if group in _preferred:
+        _preferred.remove(group)
+    _preferred.insert(0, group)
+
+
+def _in_group(name: str, group: str) -> bool:
+    return name in _BOTH or (group in _GROUPS_OF[name] if name in _GROUPS_OF else group == "main")
 
 
 def _group_of(name: str) -> str:
-    if name in _BOTH:                 # from whichever library is loaded (none yet: the one last asked for, or the small one)
-        return next(iter(_libs), "hybrid")
-    return _home(name)
+    if name in _BOTH:                 # from whichever library is loaded (none yet: the preferred one, or the small one)
+        return next(iter(_libs), _preferred[0] if _preferred else "hybrid")
+    homes = _GROUPS_OF.get(name)
+    if homes is None:
+        return "main"
+    for group in _libs:               # a loaded library that holds it
+        if group in homes:
+            return group
+    return next((g for g in _preferred if g in homes), homes[0])
 
 
 def register_signature(name: str, argtypes: list) -> None:
@@ -145,7 +185,7 @@ def load(group: str = "main") -> ctypes.CDLL:
             path = _build.build(group=group)
             lib = ctypes.CDLL(str(path))
             for name, argtypes in _SIGNATURES.items():
-                if name in _BOTH or _home(name) == group:
+                if _in_group(name, group):
                     _bind(lib, name, argtypes)
             _libs[group] = lib
     return _libs[group]

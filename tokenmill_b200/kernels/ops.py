@@ -1031,6 +1031,56 @@ def glu_routed(gu: torch.Tensor, dense_w: torch.Tensor, act: torch.Tensor, E: in
     return act
 
 
+def router_logits(x: torch.Tensor, w: torch.Tensor, w_low: torch.Tensor | None = None) -> torch.Tensor:
+    """x [T, H] . w [n, H]^T in 32-bit: this library's 32-bit product for float32 inputs; for bfloat16 inputs the library's
+    product of x with ``w_low``, a bfloat16 copy of w that holds the same values, with its 32-bit accumulator as the result
+    (products of two bfloat16 numbers are exact in 32-bit), or x converted and the 32-bit product when there is no such copy."""
+    if x.dtype == torch.float32:
+        return linear(x, w)
+    if w_low is not None:
+        return torch.mm(x, w_low.t(), out_dtype=torch.float32)
+    return linear(x.float(), w)
+
+
+def moe_choose(logits: torch.Tensor, correction: torch.Tensor | None, top: int, groups: int = 1, keep: int = 1,
+               identity: int = 0):
+    """logits [T, n] float32 over experts and identity outputs -> (top_idx [T, top] int32, top_w [T, top], dense_w [T, n],
+    identity_w [T] float32). Scores are a softmax over all n; the choice is by score + correction, restricted to the best
+    ``keep`` of ``groups`` equal groups of neighbours; weights are the chosen scores over their sum; identity_w sums the
+    weights of chosen outputs among the last ``identity``."""
+    T, n = logits.shape
+    dev = logits.device
+    idx = torch.empty((T, top), dtype=torch.int32, device=dev)
+    tw = torch.empty((T, top), dtype=torch.float32, device=dev)
+    dense = torch.empty((T, n), dtype=torch.float32, device=dev)
+    idw = torch.empty((T,), dtype=torch.float32, device=dev)
+    if correction is not None and correction.numel() != n:
+        raise lib.KernelError("moe_choose: the correction has one number per router output")
+    lib.call("tm_moe_choose", _req(logits, "logits", torch.float32), _opt(correction, "correction", torch.float32),
+             idx.data_ptr(), tw.data_ptr(), dense.data_ptr(), idw.data_ptr(), T, n, int(top), int(groups), int(keep),
+             int(identity), _stream())
+    return idx, tw, dense, idw
+
+
+def act_routed(up: torch.Tensor, dense_w: torch.Tensor, act: torch.Tensor, E: int, F: int) -> torch.Tensor:
+    """up [T, E * F] -> act [T, E * F] = relu(up)^2 * weight of the expert (dense_w [T, >= E] float32), zero where not chosen."""
+    T = up.shape[0]
+    if up.shape[1] != E * F or act.shape != (T, E * F) or dense_w.shape[0] != T or dense_w.shape[1] < E:
+        raise lib.KernelError("act_routed: shapes do not fit")
+    lib.call("tm_act_routed", _code(up.dtype), _req(up, "up"), _req(dense_w, "dense_w", torch.float32), dense_w.shape[1],
+             _req(act, "act", up.dtype), T, E, F, _stream())
+    return act
+
+
+def add_scaled_rows(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """out[t] += w[t] * x[t]; out and x [T, H] in the same dtype, w [T] float32."""
+    if out.shape != x.shape or out.dtype != x.dtype or w.numel() != out.shape[0]:
+        raise lib.KernelError("add_scaled_rows: shapes do not fit")
+    lib.call("tm_add_scaled_rows", _code(out.dtype), _req(out, "out"), _req(x, "x"), _req(w, "w", torch.float32), out.shape[0],
+             out.shape[1], _stream())
+    return out
+
+
 # --- gated convolutional blocks, windowed attention with a sink, matrix memory --------------------------------
 
 GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
@@ -1115,11 +1165,19 @@ def head_norm_gate(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, ep
 def qk_norm_rope_write(proj: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int, rot_dims: int,
                        wq: torch.Tensor | None, wk: torch.Tensor | None, eps: float, positions: torch.Tensor,
                        cos: torch.Tensor, sin: torch.Tensor, slot_map: torch.Tensor | None, q_out: torch.Tensor,
-                       cache: torch.Tensor | None, gate_out: torch.Tensor | None) -> None:
-    """proj [T, >= H d + G d + G dv (+ H)] float32 (rows may be strided) -> q_out [T, H d] normed and rotated, the
-    token's cache row [k | v], gate_out [T, H] = sigmoid of the last H columns."""
+                       cache: torch.Tensor | None, gate_out: torch.Tensor | None, has_kv: bool = True,
+                       q_temp: tuple[float, int] | None = None) -> None:
+    """proj [T, >= H d + G d + G dv (+ gate columns)] float32 (rows may be strided) -> q_out [T, H d] normed and rotated,
+    the token's cache row [k | v], gate_out [T, H] or [T, H dv] = sigmoid of the last columns. ``has_kv`` False: the row
+    is [q | g] only (a layer that reads another layer's keys and values). ``q_temp`` (coef, every): the query is
+    multiplied by 1 + coef ln(floor((p + 1) / every) + 1) at position p."""
     T = proj.shape[0]
-    need = heads * dim + kv_heads * (dim + vdim) + (heads if gate_out is not None else 0)
+    gate_cols = gate_out.shape[1] if gate_out is not None else 0
+    need = heads * dim + (kv_heads * (dim + vdim) if has_kv else 0) + gate_cols
+    if gate_cols not in (0, heads, heads * vdim) or (not has_kv and (cache is not None or wk is not None)):
+        raise lib.KernelError("qk_norm_rope_write: the gate has one column per head or per output number; a row without "
+                              "keys writes no cache")
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
     if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[1] < need or q_out.shape != (T, heads * dim) or \
             cos.shape[1] * 2 != rot_dims or (cache is not None and cache.shape[-1] != kv_heads * (dim + vdim)):
         raise lib.KernelError("qk_norm_rope_write: shapes do not fit")
@@ -1128,8 +1186,8 @@ def qk_norm_rope_write(proj: torch.Tensor, *, heads: int, kv_heads: int, dim: in
              _opt(wq, "wq", torch.float32), _opt(wk, "wk", torch.float32), float(eps),
              _req(positions, "positions", torch.int32), _req(cos, "cos", torch.float32), _req(sin, "sin", torch.float32),
              cos.shape[0], _opt(slot_map, "slot_map", torch.int32) if cache is not None else None, _req(q_out, "q_out"),
-             _opt(cache, "cache", dt), _opt(gate_out, "gate_out", torch.float32), T, _tc_flag(proj.device).data_ptr(),
-             _stream())
+             _opt(cache, "cache", dt), _opt(gate_out, "gate_out", torch.float32), gate_cols, int(bool(has_kv)), coef, every,
+             T, _tc_flag(proj.device).data_ptr(), _stream())
 
 
 SINK_TILE_ROWS = 32
@@ -1148,13 +1206,15 @@ def sink_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tens
                    scale: float, softcap: float, window: int, keep_first: int, sink: bool,
                    tensor_cores: bool = False, n_splits: int = 1, part: torch.Tensor | None = None) -> torch.Tensor:
     """q [T, H d]; cache [pages, page_size, 1, G d + G dv]; tiles of 32 (``tensor_cores``: 64) (token, head in group)
-    rows of one request; gate [T, H] float32 or None; out [T, H dv]. ``n_splits`` > 1 (tensor cores only): a tile's
+    rows of one request; gate [T, H] (or [T, H dv]: one per output number) float32 or None; out [T, H dv]. ``n_splits`` > 1 (tensor cores only): a tile's
     key blocks dealt out over that many blocks and merged, through ``part``, float32 scratch of
     n_tiles * G * n_splits * 64 * (dv + 2) numbers."""
     T = q.shape[0]
     row = kv_heads * (dim + vdim)
-    if cache.shape[-1] != row or q.shape != (T, heads * dim) or out.shape != (T, heads * vdim):
+    if cache.shape[-1] != row or q.shape != (T, heads * dim) or out.shape != (T, heads * vdim) or \
+            (gate is not None and tuple(gate.shape) not in ((T, heads), (T, heads * vdim))):
         raise lib.KernelError("sink_attention: shapes do not fit")
+    wide = int(gate is not None and gate.shape[1] != heads)
     if tensor_cores:
         part_o = part_ml = None
         if n_splits > 1:
@@ -1168,14 +1228,14 @@ def sink_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tens
                  _req(tile_seq, "tile_seq", torch.int32), _req(tile_row0, "tile_row0", torch.int32), int(n_tiles),
                  _opt(gate, "gate", torch.float32), _req(out, "out", torch.bfloat16), heads, kv_heads, dim, vdim,
                  cache.shape[1], float(scale), float(softcap), int(window), int(keep_first), int(bool(sink)),
-                 int(n_splits), part_o, part_ml, _stream())
+                 int(n_splits), part_o, part_ml, wide, _stream())
         return out
     lib.call("tm_sink_attention", _code(q.dtype), _req(q, "q"), _req(cache, "cache", q.dtype), row, kv_heads * dim,
              _req(block_table, "block_table", torch.int32), block_table.stride(0), _req(cu_q, "cu_q", torch.int32),
              _req(kv_before, "kv_before", torch.int32), _req(tile_seq, "tile_seq", torch.int32),
              _req(tile_row0, "tile_row0", torch.int32), int(n_tiles), _opt(gate, "gate", torch.float32),
              _req(out, "out", q.dtype), heads, kv_heads, dim, vdim, cache.shape[1], float(scale), float(softcap),
-             int(window), int(keep_first), int(bool(sink)), _stream())
+             int(window), int(keep_first), int(bool(sink)), wide, _stream())
     return out
 
 
@@ -1239,3 +1299,85 @@ def matrix_memory(proj: torch.Tensor, *, q_col: int, k_col: int, v_col: int, i_c
 def matrix_memory_slice_records(n_tokens: int, n_seqs: int, slice_len: int) -> int:
     """Slice records a step needs: request s owns records cu_q[s] // slice_len + s onwards."""
     return n_tokens // slice_len + n_seqs
+
+
+# --- several residual streams behind a norm, selective scan, linear attention with a decay --------------------
+
+STREAM_NORMS = {"dyt": 0, "rms": 1}
+MAX_STREAMS = 8
+
+
+def stream_norm(resid: torch.Tensor, streams: int, out: torch.Tensor, *, kind: str, weight: torch.Tensor,
+                bias: torch.Tensor | None = None, alpha: torch.Tensor | None = None, eps: float = 0.0,
+                ids: torch.Tensor | None = None, table: torch.Tensor | None = None, positions: torch.Tensor | None = None,
+                pos_table: torch.Tensor | None = None, branch: torch.Tensor | None = None, branch2: torch.Tensor | None = None,
+                row_scale: torch.Tensor | None = None, mix: torch.Tensor | None = None, out_w: torch.Tensor | None = None,
+                in_w: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """resid [T, streams * H] float32: the streams of every token side by side. Starts them all as table[ids] (+
+    pos_table[positions]), or takes in y = branch + row_scale * branch2: x_t <- sum_s mix[s, t] x_s + out_w[t] y (no mix:
+    x_t <- x_t + y); reads u = sum_s in_w[s] x_s (no in_w: the sum) and writes out = norm(u): ``dyt`` tanh(alpha u) w + b, or
+    ``rms``. With ``rows`` only those rows are normed and the residual stays as it is."""
+    H = out.shape[-1]
+    n_rows = rows.numel() if rows is not None else resid.shape[0]
+    if kind not in STREAM_NORMS or resid.shape[-1] != streams * H or out.shape[0] < n_rows or weight.numel() != H or \
+            (ids is None) != (table is None) or (pos_table is None) != (positions is None and pos_table is None) or \
+            (kind == "dyt" and (alpha is None or alpha.numel() != 1)) or not 1 <= streams <= MAX_STREAMS:
+        raise lib.KernelError("stream_norm: shapes do not fit")
+    if (mix is not None and mix.numel() != streams * streams) or (out_w is not None and out_w.numel() != streams) or \
+            (in_w is not None and in_w.numel() != streams) or (mix is None and streams > 1 and (branch is not None or branch2 is not None)):
+        raise lib.KernelError("stream_norm: mix is [streams, streams], out_w and in_w [streams]; several streams need a mix")
+    dt = out.dtype
+    lib.call("tm_stream_norm", _code(dt), _req(resid, "resid", torch.float32), int(streams), H, _opt(ids, "ids", torch.int32),
+             _opt(table, "table", dt), _opt(positions, "positions", torch.int32) if pos_table is not None else None,
+             _opt(pos_table, "pos_table", dt), _opt(branch, "branch", dt), _opt(branch2, "branch2", dt),
+             row_scale.data_ptr() if row_scale is not None else None, row_scale.stride(0) if row_scale is not None else 0,
+             _opt(mix, "mix", torch.float32), _opt(out_w, "out_w", torch.float32), _opt(in_w, "in_w", torch.float32),
+             _opt(rows, "rows", torch.int32), STREAM_NORMS[kind], _opt(alpha, "alpha", torch.float32),
+             _req(weight, "weight", torch.float32), _opt(bias, "bias", torch.float32), float(eps), _req(out, "out"), n_rows, _stream())
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap), in place (float32)."""
+    lib.call("tm_softcap", _req(x, "x", torch.float32), x.numel(), float(cap), _stream())
+    return x
+
+
+def selective_scan(x: torch.Tensor, z: torch.Tensor, z_col: int, dbc: torch.Tensor, w_dt: torch.Tensor, b_dt: torch.Tensor,
+                   A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, state_off: int, cu_q: torch.Tensor,
+                   state_slots: torch.Tensor, out: torch.Tensor, *, n_seqs: int, rank: int, N: int) -> torch.Tensor:
+    """x [T, inner] (convolved, activated); z: the gate's pre-activations at columns z_col .. z_col + inner of a matrix in x's
+    dtype; dbc [T, rank + 2 N] float32 = [low | B | C]; w_dt [inner, rank], b_dt [inner], A_log [inner, N], D [inner] float32;
+    a request's states [inner, N] live ``state_off`` floats into its slot. out [T, inner] = (scan + D x) silu(z)."""
+    T, inner = x.shape
+    if out.shape != x.shape or dbc.shape != (T, rank + 2 * N) or z.shape[0] != T or z_col + inner > z.shape[1] or \
+            tuple(w_dt.shape) != (inner, rank) or tuple(A_log.shape) != (inner, N) or b_dt.numel() != inner or D.numel() != inner or \
+            state.shape[1] < state_off + inner * N or z.dtype != x.dtype or z.stride(1) != 1:
+        raise lib.KernelError("selective_scan: shapes do not fit")
+    lib.call("tm_selective_scan", _code(x.dtype), _req(x, "x"), inner, z.data_ptr(), z.stride(0), int(z_col),
+             _req(dbc, "dbc", torch.float32), dbc.stride(0), int(rank), int(N), _req(w_dt, "w_dt", torch.float32),
+             _req(b_dt, "b_dt", torch.float32), _req(A_log, "A_log", torch.float32), _req(D, "D", torch.float32),
+             _req(state, "state", torch.float32), state.stride(0), int(state_off), _req(cu_q, "cu_q", torch.int32),
+             _req(state_slots, "state_slots", torch.int32), _req(out, "out", x.dtype), int(n_seqs), _stream())
+    return out
+
+
+DECAY_ACTIVATIONS = {None: 0, "none": 0, "silu": 1}
+
+
+def decay_memory(proj: torch.Tensor, *, q_col: int, k_col: int, v_col: int, activation: str | None, decay: torch.Tensor,
+                 state: torch.Tensor, state_off: int, cu_q: torch.Tensor, state_slots: torch.Tensor, y: torch.Tensor,
+                 n_seqs: int, heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """proj [T, P] float32 (rows may be strided) with q, k (heads x dim) and v (heads x vdim) at the given columns, each
+    through ``activation``; per head S <- decay S + k v^T, y = S^T q; a request's memories [heads, dim, vdim] live
+    ``state_off`` floats into its slot; y [T, heads * vdim] float32."""
+    T = proj.shape[0]
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or y.shape != (T, heads * vdim) or decay.numel() != heads or \
+            max(q_col, k_col) + heads * dim > proj.shape[1] or v_col + heads * vdim > proj.shape[1] or \
+            state.shape[1] < state_off + heads * dim * vdim or activation not in DECAY_ACTIVATIONS:
+        raise lib.KernelError("decay_memory: shapes do not fit")
+    lib.call("tm_decay_memory", proj.data_ptr(), proj.stride(0), int(q_col), int(k_col), int(v_col), DECAY_ACTIVATIONS[activation],
+             _req(decay, "decay", torch.float32), _req(state, "state", torch.float32), state.stride(0), int(state_off),
+             _req(cu_q, "cu_q", torch.int32), _req(state_slots, "state_slots", torch.int32), _req(y, "y", torch.float32),
+             int(n_seqs), heads, dim, vdim, _stream())
+    return y

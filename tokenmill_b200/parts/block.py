@@ -30,24 +30,37 @@ class Pending:
     gate: torch.Tensor | None = None         # 32-bit pre-activations of a gate on the branch, and the gate's bias
     gate_bias: torch.Tensor | None = None    # (norms that take them: GatedAddRMSNorm)
     table_scale: float = 1.0                  # multiplier of the embedding rows (norms that read ``table``)
+    positions: torch.Tensor | None = None    # a learned vector per position, added to the embedding rows
+    pos_table: torch.Tensor | None = None    # (norms that take them: DynamicTanhNorm)
+    row_scale: torch.Tensor | None = None    # [T] float32: branch2 enters as row_scale[t] * branch2[t] (the same norms)
+    stream_mix: torch.Tensor | None = None   # several residual streams: how the branch enters them, x_t <- sum_s
+    stream_out: torch.Tensor | None = None   # mix[s, t] x_s + out[t] y (blocks with hyper-connections set them)
 
     @classmethod
-    def of(cls, y: torch.Tensor) -> "Pending":
+    def of(cls, y) -> "Pending":
         """A part's output: [T, H] in the activation dtype, or [n, T, H] float32 partial products of a
         matrix product whose K range was cut (the norm that follows adds them up in index order), or None
-        when the part has added its output into the stream itself."""
+        when the part has added its output into the stream itself; a ``Pending`` passes through."""
         if y is None:
             return cls()
+        if isinstance(y, cls):
+            return y
         return cls(partials=y) if y.dim() == 3 else cls(branch=y)
 
     def kwargs(self) -> dict:
         kw = {"branch": self.branch, "partials": self.partials, "ids": self.ids, "table": self.table}
-        if self.branch2 is not None or self.scale != 1.0:
+        if self.row_scale is not None:
+            kw.update(branch2=self.branch2, row_scale=self.row_scale)
+        elif self.branch2 is not None or self.scale != 1.0:
             kw.update(branch2=self.branch2, scale=self.scale)
         if self.gate is not None:
             kw.update(gate=self.gate, gate_bias=self.gate_bias)
         if self.table_scale != 1.0 and self.table is not None:
             kw.update(table_scale=self.table_scale)
+        if self.pos_table is not None and self.table is not None:
+            kw.update(positions=self.positions, pos_table=self.pos_table)
+        if self.stream_mix is not None:
+            kw.update(stream_mix=self.stream_mix, stream_out=self.stream_out)
         return kw
 
 
@@ -194,6 +207,74 @@ class ConvGatedBlock:
         return Pending(branch=self.feed_forward.forward(hc, step), gate=gate, gate_bias=self.b_gate[1])
 
 
+class HyperConnectionBlock:
+    """Pre-norm block over several residual streams (hyper-connections). A token carries ``streams`` copies x_1 .. x_s of
+    the stream, all equal where the model starts. Sublayer q (1: mixer, 2: feed-forward) reads them as
+    ``u = sum_s in_q[s] x_s``, runs on ``norm(u)``, and its result y enters all streams at once from the old ones:
+    ``x_t <- sum_s mix_q[s, t] x_s + out_q[t] y`` (mix is indexed [from, to]). The tensors are ``hc1.in``, ``hc1.out``,
+    ``hc1.mix`` and ``hc2.*`` of the layer, 32-bit. Neither the read nor the write is a pass of its own: the norm in
+    front of a sublayer (a norm that takes ``stream_in`` / ``stream_mix`` / ``stream_out``, such as ``DynamicTanhNorm``)
+    first takes in the previous sublayer's result and then reads, in one pass over the row. With one stream and
+    mix = out = in = 1 this is the plain pre-norm block. The feed-forward may be absent. A feed-forward that can hand
+    over its result in two pieces (``forward_parts``: a branch, and a second one with a weight per token) is taken that
+    way, so that the sum happens in the same pass."""
+
+    wants_run_context = True
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, *, hidden_size: int, streams: int,
+                 names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
+        if streams < 1:
+            raise ValueError(f"a block has at least one residual stream, got {streams}")
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.hidden_size, self.streams = hidden_size, int(streams)
+        self.dtype, self.device = dtype, device
+        self.names = {"in1": "hc1.in", "out1": "hc1.out", "mix1": "hc1.mix", "in2": "hc2.in", "out2": "hc2.out",
+                      "mix2": "hc2.mix", **(names or {})}
+        self.w_in: list = [None, None]
+        self.w_out: list = [None, None]
+        self.w_mix: list = [None, None]
+
+    def _sides(self) -> list[int]:
+        return [1] if self.feed_forward is None else [1, 2]
+
+    def weight_specs(self):
+        from .spec import WeightSpec
+        s, n, out = self.streams, self.names, []
+        for i in self._sides():
+            out += [WeightSpec(n[f"in{i}"], (s,), dtype="float32", init=("normal", 0.2, 1.0 / s)),
+                    WeightSpec(n[f"out{i}"], (s,), dtype="float32", init=("normal", 0.2, 1.0)),
+                    WeightSpec(n[f"mix{i}"], (s, s), dtype="float32", init=("normal", 0.2, 1.0 / s))]
+        return out
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        for i in self._sides():
+            self.w_in[i - 1] = tensors[self.names[f"in{i}"]]
+            self.w_out[i - 1] = tensors[self.names[f"out{i}"]]
+            self.w_mix[i - 1] = tensors[self.names[f"mix{i}"]]
+
+    def _written(self, y, side: int) -> Pending:
+        out = Pending.of(y)
+        if out.partials is not None:
+            raise NotImplementedError("several residual streams take branch outputs, not partial products")
+        out.stream_mix, out.stream_out = self.w_mix[side], self.w_out[side]
+        return out
+
+    def forward(self, resid: torch.Tensor, pending: Pending, step: StepInputs, cache: LayerCache) -> Pending:
+        h = self.mixer_norm.forward(resid, stream_in=self.w_in[0], **pending.kwargs())
+        out = self._written(self.mixer.forward(h, step, cache), 0)
+        if self.feed_forward is None:
+            return out
+        h = self.feed_forward_norm.forward(resid, stream_in=self.w_in[1], **out.kwargs())
+        if callable(getattr(self.feed_forward, "forward_parts", None)):
+            branch, branch2, row_scale = self.feed_forward.forward_parts(h, step)
+            y = Pending(branch=branch, branch2=branch2, row_scale=row_scale) if branch2 is not None else branch
+        else:
+            y = self.feed_forward.forward(h, step)
+        return self._written(y, 1)
+
+
 register_block("conv_gated", ConvGatedBlock)
+register_block("hyper_connections", HyperConnectionBlock)
 register_block("pre_norm", PreNormBlock)
 register_block("parallel_shift", ParallelShiftBlock)

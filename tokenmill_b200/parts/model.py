@@ -93,6 +93,8 @@ class DecoderModel:
         self.final_norm = _build("norm", spec.final_norm, dtype, device)
         self._named.append((spec.final_norm_prefix, self.final_norm))
         self.embedding: torch.Tensor | None = None
+        self.position_table: torch.Tensor | None = None
+        self.layer_tap = None       # debugging aid: called as (run-order position, residual, pending) after every block
         self.output_weight: torch.Tensor | None = None
 
     # --- weights --------------------------------------------------------------------------------
@@ -102,6 +104,8 @@ class DecoderModel:
         draws them in this order)."""
         s = self.spec
         out = [WeightSpec(s.embedding_name, (s.vocab_size, s.hidden_size))]
+        if s.position_table_name is not None:
+            out.append(WeightSpec(s.position_table_name, (s.max_positions, s.hidden_size)))
         for prefix, part in self._named:
             out += [WeightSpec(_full_name(prefix, w.name), w.shape, w.dtype, w.init) for w in part.weight_specs()]
         if s.lm_head_name is not None:
@@ -111,6 +115,8 @@ class DecoderModel:
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         s = self.spec
         self.embedding = tensors[s.embedding_name]
+        if s.position_table_name is not None:
+            self.position_table = tensors[s.position_table_name]
         self.output_weight = self.embedding if s.lm_head_name is None else tensors[s.lm_head_name]
         for prefix, part in self._named:
             part.bind({w.name: tensors[_full_name(prefix, w.name)] for w in part.weight_specs()})
@@ -151,7 +157,7 @@ class DecoderModel:
         per_layer = max((part_activation_bytes(b.mixer, n_tokens, H) +
                          (part_activation_bytes(b.feed_forward, n_tokens, H) if b.feed_forward is not None else 0)
                          for b in self.blocks), default=0)
-        return n_tokens * H * 8 + per_layer
+        return n_tokens * H * 4 * (1 + self.spec.streams) + per_layer
 
     # --- cache needs ----------------------------------------------------------------------------
 
@@ -195,8 +201,8 @@ class DecoderModel:
         s = self.spec
         parts = [p for blk in self.blocks for p in (blk, blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm)
                  if p is not None]
-        if self.dtype != torch.bfloat16 or s.embedding_scale != 1.0 or \
-                not all(hasattr(p, "emit") for p in parts + [self.final_norm]):
+        if self.dtype != torch.bfloat16 or s.embedding_scale != 1.0 or s.streams != 1 or s.position_table_name is not None or \
+                s.logit_softcap or not all(hasattr(p, "emit") for p in parts + [self.final_norm]):
             return None
         b = ProgramBuilder(self.device, self.dtype)
         try:
@@ -217,11 +223,17 @@ class DecoderModel:
     def forward(self, step: StepInputs, caches: list[LayerCache]) -> torch.Tensor:
         """Run the step's tokens; returns logits [n_want, vocab] float32."""
         s = self.spec
-        resid = torch.empty((step.n_tokens, s.hidden_size), dtype=torch.float32, device=self.device)
+        # (a token's residual streams lie side by side in its row)
+        resid = torch.empty((step.n_tokens, s.streams * s.hidden_size), dtype=torch.float32, device=self.device)
         pending = Pending(ids=step.token_ids, table=self.embedding, table_scale=s.embedding_scale)
+        if self.position_table is not None:
+            pending.positions, pending.pos_table = step.positions, self.position_table
         for pos, entry in enumerate(s.run_order):
             pending = self.blocks[entry.layer].forward(resid, pending, step, caches[pos])
+            if self.layer_tap is not None:
+                self.layer_tap(pos, resid, pending)
         if step.n_want == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.device)
         hidden = self.final_norm.forward(resid, rows=step.want_rows, **pending.kwargs())
-        return ops.linear(hidden, self.output_weight, out_dtype=torch.float32)
+        logits = ops.linear(hidden, self.output_weight, out_dtype=torch.float32)
+        return ops.softcap_(logits, s.logit_softcap) if s.logit_softcap else logits

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
+from ..kernels import lib, ops
 from ..registry import register_norm
 from .spec import WeightSpec
 
@@ -123,6 +123,58 @@ class GatedAddRMSNorm:
                                      ids=ids, table=table, table_scale=table_scale, rows=rows)
 
 
+class DynamicTanhNorm:
+    """Dynamic Tanh in the place of a norm: ``tanh(alpha * x) * w + b`` with a learned scalar ``alpha``, a weight and a
+    bias vector; no mean, no variance, no eps. Tensors: the weight under the part's own name, ``b`` and ``alpha`` beside
+    it. 32-bit throughout, one rounding.
+
+    It reads a residual of one or several streams (``streams`` copies of the row side by side, ``resid`` [T, streams * H]):
+    on the way it takes in the previous sublayer's result, ``x_t <- sum_s stream_mix[s, t] x_s + stream_out[t] y`` (one
+    stream without a mix: ``x += y``), with ``y = branch + row_scale * branch2``; or starts every stream as
+    ``table[ids] + pos_table[positions]``; then norms ``u = sum_s stream_in[s] x_s`` (no ``stream_in``: the sum of the
+    streams, which is what a model's last norm reads). ``kind="rms"`` keeps all of that with an RMS norm (weight only)."""
+
+    def __init__(self, *, hidden_size: int, streams: int = 1, kind: str = "dyt", eps: float = 0.0,
+                 names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
+        if kind not in ops.STREAM_NORMS or not 1 <= streams <= ops.MAX_STREAMS:
+            raise ValueError(f"norm kinds {sorted(ops.STREAM_NORMS)} over 1 to {ops.MAX_STREAMS} streams are built, got "
+                             f"{kind!r} over {streams}")
+        lib.prefer("streams")
+        self.hidden_size, self.streams, self.kind, self.eps = hidden_size, int(streams), kind, float(eps)
+        self.dtype, self.device = dtype, device
+        self.names = {"weight": "", "bias": "b", "alpha": "alpha", **(names or {})}
+        self.weight = self.bias = self.alpha = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        n, H = self.names, self.hidden_size
+        specs = [WeightSpec(n["weight"], (H,), dtype="float32", init=("ones_plus_normal", 0.1))]
+        if self.kind == "dyt":
+            specs += [WeightSpec(n["bias"], (H,), dtype="float32", init=("normal", 0.1)),
+                      WeightSpec(n["alpha"], (), dtype="float32", init=("normal", 0.05, 0.6))]
+        return specs
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.names["weight"]]
+        if self.kind == "dyt":
+            self.bias, self.alpha = tensors[self.names["bias"]], tensors[self.names["alpha"]].reshape(1)
+
+    def forward(self, resid: torch.Tensor, out: torch.Tensor | None = None, *, branch: torch.Tensor | None = None,
+                branch2: torch.Tensor | None = None, row_scale: torch.Tensor | None = None,
+                partials: torch.Tensor | None = None, ids: torch.Tensor | None = None, table: torch.Tensor | None = None,
+                positions: torch.Tensor | None = None, pos_table: torch.Tensor | None = None,
+                rows: torch.Tensor | None = None, stream_mix: torch.Tensor | None = None,
+                stream_out: torch.Tensor | None = None, stream_in: torch.Tensor | None = None) -> torch.Tensor:
+        if partials is not None:
+            raise NotImplementedError("this norm takes branch outputs, not partial products")
+        n = rows.numel() if rows is not None else resid.shape[0]
+        if out is None:
+            out = torch.empty((n, self.hidden_size), dtype=self.dtype, device=resid.device)
+        return ops.stream_norm(resid, self.streams, out, kind=self.kind, weight=self.weight, bias=self.bias, alpha=self.alpha,
+                               eps=self.eps, ids=ids, table=table, positions=positions, pos_table=pos_table, branch=branch,
+                               branch2=branch2, row_scale=row_scale, mix=stream_mix, out_w=stream_out, in_w=stream_in, rows=rows)
+
+
+register_norm("dyt", DynamicTanhNorm)
 register_norm("rmsnorm", RMSNorm)
 register_norm("rmsnorm_gated", GatedAddRMSNorm)
 register_norm("rmsnorm32", RMSNorm32)

@@ -8,6 +8,11 @@ chosen logits alone; the output is the weighted sum of the chosen experts' outpu
 matrices are held as one matrix [E, 2, F, H] and their down matrices side by side along K as [H, E F]: the
 activation kernel writes silu(gate) * up * weight for the chosen experts and exact zeros for the others, so the
 second product sums the chosen experts with their weights in its 32-bit accumulator.
+
+``ChoiceRoutedExperts``: E small feed-forwards ``W_down relu(W_up h)^2`` and ``identity`` further router outputs without
+tensors, whose result is the input h itself. Scores are a softmax over ALL router outputs; the choice is made by score +
+``correction`` (a learned vector that does not enter the weights), among the best ``keep`` of ``groups`` equal groups of
+neighbouring outputs (a group's score: its largest choice score); the weights are the chosen scores divided by their sum.
 """
 
 from __future__ import annotations
@@ -95,5 +100,70 @@ class RoutedExperts:
         return ops.linear(act, self.w_down)
 
 
+class ChoiceRoutedExperts:
+    def __init__(self, *, hidden_size: int, expert_size: int, num_experts: int, top: int, identity: int = 0, groups: int = 1,
+                 keep: int = 1, names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
+        n = num_experts + identity
+        if num_experts < 1 or identity < 0:
+            raise ValueError("at least one expert with tensors, and no negative count of identity outputs")
+        if groups < 1 or n % groups or not 1 <= keep <= groups:
+            raise ValueError(f"{n} router outputs do not form {groups} equal groups of which {keep} are kept")
+        if not 1 <= top <= keep * (n // groups):
+            raise ValueError(f"top ({top}) must lie between 1 and the outputs of the kept groups ({keep * (n // groups)})")
+        self.hidden_size, self.F, self.E, self.top, self.identity = hidden_size, expert_size, num_experts, top, identity
+        self.n, self.groups, self.keep = n, groups, keep
+        self.dtype, self.device = dtype, device
+        # {e} is the expert's number
+        self.names = {"router": "router", "correction": "correction", "up": "e{e}.up", "down": "e{e}.down", **(names or {})}
+        self.w_router = self.w_router_low = self.correction = self.w_up = self.w_down = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        H, F, n = self.hidden_size, self.F, self.names
+        specs = []
+        for e in range(self.E):
+            specs += [WeightSpec(n["up"].format(e=e), (F, H), init=("normal", 0.05)),
+                      WeightSpec(n["down"].format(e=e), (H, F), init=("normal", 0.05))]
+        specs += [WeightSpec(n["router"], (self.n, H), dtype="float32", init=("normal", 0.3)),
+                  WeightSpec(n["correction"], (self.n,), dtype="float32", init=("normal", 0.05))]
+        return specs
+
+    def activation_bytes(self, n_tokens: int) -> int:
+        elt = 4 if self.dtype == torch.float32 else 2
+        return n_tokens * ((2 * self.E * self.F + self.hidden_size) * elt + 12 * self.n)
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.w_router, self.correction = tensors[n["router"]], tensors[n["correction"]]
+        # bfloat16 runs: a bfloat16 copy of the router for the library product, if it holds the very same values
+        low = self.w_router.to(torch.bfloat16)
+        self.w_router_low = low if self.dtype == torch.bfloat16 and bool((low.float() == self.w_router).all()) else None
+        self.w_up = torch.cat([tensors[n["up"].format(e=e)] for e in range(self.E)], dim=0).contiguous()       # [E F, H]
+        self.w_down = torch.cat([tensors[n["down"].format(e=e)] for e in range(self.E)], dim=1).contiguous()   # [H, E F]
+
+    def route(self, x: torch.Tensor):
+        """(chosen outputs [T, top] int32, their weights [T, top], dense weights [T, E + identity], summed weight of the
+        chosen identity outputs [T]), all weights float32."""
+        logits = ops.router_logits(x, self.w_router, self.w_router_low)
+        return ops.moe_choose(logits, self.correction, self.top, self.groups, self.keep, self.identity)
+
+    def forward_parts(self, x: torch.Tensor, step: StepInputs | None = None):
+        """(the experts' weighted sum [T, H], x or None, the identity outputs' weight per token or None): the result is
+        the first plus the third times the second; a norm that takes two branches adds them in its own pass."""
+        T = x.shape[0]
+        _idx, _w, dense, id_w = self.route(x)
+        up = ops.linear(x, self.w_up)                                            # [T, E * F]
+        act = torch.empty((T, self.E * self.F), dtype=self.dtype, device=x.device)
+        ops.act_routed(up, dense, act, self.E, self.F)
+        out = ops.linear(act, self.w_down)
+        return (out, x, id_w) if self.identity else (out, None, None)
+
+    def forward(self, x: torch.Tensor, step: StepInputs | None = None) -> torch.Tensor:
+        out, x2, id_w = self.forward_parts(x, step)
+        if x2 is None:
+            return out
+        return ops.add_scaled_rows(out, x2, id_w)
+
+
+register_feed_forward("routed_choice", ChoiceRoutedExperts)
 register_feed_forward("relu2", SquaredReluFeedForward)
 register_feed_forward("routed_experts", RoutedExperts)

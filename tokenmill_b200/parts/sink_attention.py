@@ -10,7 +10,11 @@
 * a softmax with one added to the denominator, p_j = exp(s_j) / (1 + sum exp(s_j)): a sink of score 0 without a
   value (``sink``);
 * a per-head output gate sigmoid(W_g h), one number per head, read from the same input as the projections
-  (``head_gate``).
+  (``head_gate``), or a gate of one number per output number, applied to the heads side by side before the output
+  projection (``value_gate``);
+* a query temperature: q is multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)`` at position p (``q_temp``);
+* no keys and values of its own (``shares_kv``): the layer has no k and v tensors and reads the cache of another
+  layer with the same head counts and sizes (the run order's ``cache_of``), with its own queries, mask and gate.
 
 Projections q, k, v (and g) are held as one matrix whose product keeps its 32-bit accumulator; one kernel norms,
 rotates and writes the token's cache row ``[k | v]`` (a paged cache of one plane whose row holds all key heads, then
@@ -38,6 +42,7 @@ class SinkWindowAttention:
     def __init__(self, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, scale: float,
                  position: PartSpec | None, rot_dims: int = 0, window: int | None = None, keep_first: int = 0,
                  softcap: float = 0.0, sink: bool = True, qk_norm: bool = True, head_gate: bool = True, eps: float = 1e-6,
+                 value_gate: bool = False, q_temp: tuple[float, int] | None = None, shares_kv: bool = False,
                  names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
         if num_heads % num_kv_heads:
             raise ValueError(f"heads ({num_heads}) must be a multiple of kv heads ({num_kv_heads})")
@@ -47,6 +52,14 @@ class SinkWindowAttention:
         self.scale, self.softcap, self.eps = float(scale), float(softcap or 0.0), float(eps)
         self.window, self.keep_first = int(window) if window else 0, int(keep_first or 0)
         self.sink, self.qk_norm, self.head_gate = bool(sink), bool(qk_norm), bool(head_gate)
+        self.value_gate, self.shares_kv = bool(value_gate), bool(shares_kv)
+        if self.value_gate and self.head_gate:
+            raise ValueError("the output gate has one number per head or one per output number, not both")
+        if self.shares_kv and self.qk_norm:
+            raise ValueError("a layer that reads another layer's keys has no key norm of its own")
+        self.q_temp = (float(q_temp[0]), int(q_temp[1])) if q_temp else None
+        if self.q_temp is not None and self.q_temp[1] < 1:
+            raise ValueError(f"the query temperature's interval must be positive, got {self.q_temp[1]}")
         self.position = get_part("position", position.kind)(**position.params) if position is not None else None
         self.rot_dims = int(rot_dims) if self.position is not None else 0
         if self.rot_dims % 2 or self.rot_dims > head_dim:
@@ -55,7 +68,8 @@ class SinkWindowAttention:
         self.names = {"q": "q", "k": "k", "v": "v", "q_norm": "q.norm", "k_norm": "k.norm", "g": "g", "o": "o",
                       **(names or {})}
         self.q_size, self.k_size, self.v_size = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
-        self.proj_width = self.q_size + self.k_size + self.v_size + (num_heads if self.head_gate else 0)
+        self.gate_cols = num_heads if self.head_gate else num_heads * value_dim if self.value_gate else 0
+        self.proj_width = self.q_size + (0 if self.shares_kv else self.k_size + self.v_size) + self.gate_cols
         # bfloat16 with key and value heads of 32, 64 or 128: tensor cores, 64 rows a tile; anything else (and the 32-bit
         # path): the shape-generic kernel on CUDA cores, 32 rows a tile
         self.tensor_cores = ops.sink_attention_tc_ok(dtype, head_dim, value_dim) and self.scale > 0
@@ -66,14 +80,15 @@ class SinkWindowAttention:
 
     def weight_specs(self) -> list[WeightSpec]:
         n, W = self.names, self.hidden_size
-        specs = [WeightSpec(n["q"], (self.q_size, W), init=("normal", 0.05)),
-                 WeightSpec(n["k"], (self.k_size, W), init=("normal", 0.05)),
-                 WeightSpec(n["v"], (self.v_size, W), init=("normal", 0.05))]
+        specs = [WeightSpec(n["q"], (self.q_size, W), init=("normal", 0.05))]
+        if not self.shares_kv:
+            specs += [WeightSpec(n["k"], (self.k_size, W), init=("normal", 0.05)),
+                      WeightSpec(n["v"], (self.v_size, W), init=("normal", 0.05))]
         if self.qk_norm:
             specs += [WeightSpec(n["q_norm"], (self.q_size,), dtype="float32", init=("ones_plus_normal", 0.1)),
                       WeightSpec(n["k_norm"], (self.k_size,), dtype="float32", init=("ones_plus_normal", 0.1))]
-        if self.head_gate:
-            specs.append(WeightSpec(n["g"], (self.nh, W), init=("normal", 0.05)))
+        if self.gate_cols:
+            specs.append(WeightSpec(n["g"], (self.gate_cols, W), init=("normal", 0.05)))
         specs.append(WeightSpec(n["o"], (W, self.nh * self.dv), init=("normal", 0.05)))
         return specs
 
@@ -97,7 +112,8 @@ class SinkWindowAttention:
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         n = self.names
-        rows = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]] + ([tensors[n["g"]]] if self.head_gate else [])
+        rows = [tensors[n["q"]]] + ([] if self.shares_kv else [tensors[n["k"]], tensors[n["v"]]]) + \
+            ([tensors[n["g"]]] if self.gate_cols else [])
         self.w_in = torch.cat(rows, dim=0).contiguous()
         self.w_o = tensors[n["o"]]
         if self.qk_norm:
@@ -139,15 +155,19 @@ class SinkWindowAttention:
         return self.forward_projected(ops.linear32(x, self.w_in), step, cache)
 
     def forward_projected(self, proj: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
-        """``proj`` [T, proj_width] float32 (a view of a wider product is fine): this mixer's columns [q | k | v | g]."""
+        """``proj`` [T, proj_width] float32 (a view of a wider product is fine): this mixer's columns [q | k | v | g]
+        ([q | g] for a layer that reads another layer's keys and values)."""
         T, dev = proj.shape[0], proj.device
         q = torch.empty((T, self.q_size), dtype=self.dtype, device=dev)
-        gate = torch.empty((T, self.nh), dtype=torch.float32, device=dev) if self.head_gate else None
+        gate = torch.empty((T, self.gate_cols), dtype=torch.float32, device=dev) if self.gate_cols else None
         rows = cache.k.view(-1, self.k_size + self.v_size)
+        if self.shares_kv and cache.writes:
+            raise ValueError("a layer without keys and values of its own reads another layer's cache")
         ops.qk_norm_rope_write(proj, heads=self.nh, kv_heads=self.nkv, dim=self.d, vdim=self.dv, rot_dims=self.rot_dims,
                                wq=self.g_q, wk=self.g_k, eps=self.eps, positions=step.positions, cos=self.cos, sin=self.sin,
                                slot_map=step.slot_maps[cache.group] if cache.writes else None, q_out=q,
-                               cache=rows if cache.writes else None, gate_out=gate)
+                               cache=rows if cache.writes else None, gate_out=gate, has_kv=not self.shares_kv,
+                               q_temp=self.q_temp)
         meta = step.meta[self.metadata_key()]
         heads = torch.empty((T, self.nh * self.dv), dtype=self.dtype, device=dev)
         splits, part = meta.host["n_splits"], None

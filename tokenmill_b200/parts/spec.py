@@ -110,6 +110,11 @@ class ModelSpec:
     eos_token_ids: list[int] = field(default_factory=list)
     ignored_name_patterns: tuple[str, ...] = ()   # checkpoint names that may be present and are not loaded
     embedding_scale: float = 1.0                  # the stream starts as embedding row * this (multiplied in 32-bit)
+    position_table_name: str | None = None        # a learned vector per position [max_positions, hidden], added to the
+                                                  # embedding row where the stream starts (norms that take ``pos_table``)
+    streams: int = 1                              # copies of the residual stream a token carries (hyper-connections);
+                                                  # the blocks say how they are read and written
+    logit_softcap: float = 0.0                    # logits <- cap * tanh(logits / cap); 0: none
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -100,4 +100,73 @@ class StateSpaceMixer:
         return ops.linear(gated, self.w_o)
 
 
+class SelectiveScanMixer:
+    """Selective state-space mixer in its first form (Mamba): a step size per channel and a decay per (channel, state).
+
+    ``W_in h = [x (inner) | z (inner)]``; x passes a causal convolution per channel (bias, silu). ``W_x x = [low (rank) |
+    B (N) | C (N)]``, ``dt = softplus(W_dt low + b_dt)`` per channel, ``A = -exp(A_log)`` [inner, N]. Per channel c and
+    state n, in 32-bit: ``S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n``, ``y_c = sum_n S[c, n] C_n + D_c x_c``;
+    then ``y silu(z)`` and W_o. ``W_x``'s product keeps its 32-bit accumulator and the rank-sized product with W_dt
+    happens inside the scan kernel in 32-bit, so nothing that enters the recurrence is rounded on the way.
+
+    Per request the mixer keeps, in ONE state slot of 32-bit floats: the last ``taps - 1`` inputs of the convolution
+    [(taps - 1), inner], then S [inner, N]; zero for a new request. The recurrence walks a request's tokens in order
+    whatever the cut."""
+
+    def __init__(self, *, hidden_size: int, inner: int, state_size: int, dt_rank: int, conv_taps: int,
+                 names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
+        if not 1 <= conv_taps <= 16 or state_size > 256:
+            raise ValueError("convolutions of 1 to 16 taps and up to 256 states per channel are built")
+        self.hidden_size, self.inner, self.N, self.rank, self.taps = hidden_size, inner, state_size, dt_rank, conv_taps
+        self.conv_len = (conv_taps - 1) * inner
+        self.dtype, self.device = dtype, device
+        self.names = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "x": "x", "dt": "dt", "dt_bias": "dt.b",
+                      "A_log": "A_log", "D": "D", "o": "o", **(names or {})}
+        self.w_in = self.w_conv = self.w_conv_t = self.b_conv = self.w_x = self.w_dt = self.b_dt = self.A_log = self.D = None
+        self.w_o = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        n, H, I = self.names, self.hidden_size, self.inner
+        f32 = dict(dtype="float32")
+        return [WeightSpec(n["in"], (2 * I, H), init=("normal", 0.05)),
+                WeightSpec(n["conv"], (I, self.taps), init=("normal", 0.3), **f32),
+                WeightSpec(n["conv_bias"], (I,), init=("normal", 0.1), **f32),
+                WeightSpec(n["x"], (self.rank + 2 * self.N, I), init=("normal", 0.1)),
+                WeightSpec(n["dt"], (I, self.rank), init=("normal", 0.3), **f32),
+                WeightSpec(n["dt_bias"], (I,), init=("normal", 0.5, -1.0), **f32),
+                WeightSpec(n["A_log"], (I, self.N), init=("normal", 0.5), **f32),
+                WeightSpec(n["D"], (I,), init=("ones_plus_normal", 0.2), **f32),
+                WeightSpec(n["o"], (H, I), init=("normal", 0.05))]
+
+    def cache_need(self):
+        return None
+
+    def state_need(self) -> StateNeed:
+        return StateNeed((self.conv_len + self.inner * self.N,), "float32")
+
+    def activation_bytes(self, n_tokens: int) -> int:
+        elt = 4 if self.dtype == torch.float32 else 2
+        return n_tokens * ((4 * self.inner + self.hidden_size) * elt + (self.rank + 2 * self.N) * 4)
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.w_in, self.w_x, self.w_o = tensors[n["in"]], tensors[n["x"]], tensors[n["o"]]
+        self.w_conv, self.b_conv = tensors[n["conv"]], tensors[n["conv_bias"]]
+        self.w_conv_t = self.w_conv.t().contiguous()          # [taps, inner], for the kernel's 16-byte loads
+        self.w_dt, self.b_dt, self.A_log, self.D = tensors[n["dt"]], tensors[n["dt_bias"]], tensors[n["A_log"]], tensors[n["D"]]
+
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
+        T, dev = x.shape[0], x.device
+        proj = ops.linear(x, self.w_in)                                       # [T, x | z]
+        xc = torch.empty((T, self.inner), dtype=self.dtype, device=dev)
+        ops.conv_silu_state(proj, 0, self.inner, self.w_conv, self.b_conv, cache.state, step.cu_q, step.seq_of_token,
+                            step.state_slots, xc, weight_t=self.w_conv_t if step.max_q_len >= VECTOR_CONV_FROM else None)
+        dbc = ops.linear32(xc, self.w_x)                                      # [T, low | B | C] float32
+        gated = torch.empty((T, self.inner), dtype=self.dtype, device=dev)
+        ops.selective_scan(xc, proj, self.inner, dbc, self.w_dt, self.b_dt, self.A_log, self.D, cache.state, self.conv_len,
+                           step.cu_q, step.state_slots, gated, n_seqs=step.n_seqs, rank=self.rank, N=self.N)
+        return ops.linear(gated, self.w_o)
+
+
+register_mixer("selective_scan", SelectiveScanMixer)
 register_mixer("state_space", StateSpaceMixer)
