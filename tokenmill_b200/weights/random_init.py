@@ -188,13 +188,73 @@ def _bobunex_named(name: str) -> dict | None:
     return None
 
 
+def dibizen_attention(*, heads, kv_heads, dim, vdim, scale=None, q_temp=None, kv_from=None) -> dict:
+    """The ``mixer`` entry of a Dibizen attention layer; ``q_temp`` = (coef, every) or None."""
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": float(scale if scale is not None else dim ** -0.5)}
+    if q_temp is not None:
+        m["q_temp"] = {"coef": float(q_temp[0]), "every": int(q_temp[1])}
+    if kv_from is not None:
+        m["kv_from"] = int(kv_from)
+    return m
+
+
+def dibizen_lightning(*, heads, dim, vdim, decay) -> dict:
+    """The ``mixer`` entry of a Dibizen linear-attention layer; ``decay``: one number per head."""
+    return {"heads": heads, "dim": dim, "vdim": vdim, "decay": [float(a) for a in decay]}
+
+
+def dibizen_mamba(*, inner, state, dt_rank, conv=4) -> dict:
+    """The ``mixer`` entry of a Dibizen state-space layer."""
+    return {"inner": inner, "state": state, "dt_rank": dt_rank, "conv": conv}
+
+
+def dibizen_moe(*, experts, top, ff, identity=0, groups=None) -> dict:
+    """The ``mlp`` entry of a Dibizen layer; ``groups`` = (count, keep) or None."""
+    router = {"experts": experts, "top": top, "identity": identity}
+    if groups is not None:
+        router["groups"] = {"count": groups[0], "keep": groups[1]}
+    return {"kind": "moe", "expert": {"ff": ff}, "router": router}
+
+
+def dibizen_config(*, vocab, width, layers, streams=2, eps=1e-5, max_positions=512, logit_softcap=30.0) -> dict:
+    """config.json of a Dibizen model. ``layers``: (type, mixer entry, mlp entry or None)."""
+    return {"architecture": "Dibizen", "vocab": vocab, "width": width, "norm": {"eps": eps}, "streams": streams,
+            "max_positions": max_positions, "logit_softcap": float(logit_softcap),
+            "layers": [{"type": kind, "mixer": mixer, "mlp": mlp} for kind, mixer, mlp in layers]}
+
+
+def _dibizen_named(name: str) -> dict | None:
+    A, L, M, E = dibizen_attention, dibizen_lightning, dibizen_mamba, dibizen_moe
+    if name == "dibizen-tiny-a":     # three streams; a layer that reads an earlier layer's keys; a layer without feed-forward
+        att = dict(heads=4, kv_heads=2, dim=12, vdim=20, scale=0.3, q_temp=(0.7, 16))
+        return dibizen_config(vocab=173, width=48, streams=3, max_positions=300, logit_softcap=8.0, layers=[
+            ("attention", A(**att), E(experts=6, top=2, ff=24, identity=2, groups=(4, 2))),
+            ("mamba1", M(inner=72, state=12, dt_rank=5, conv=3), None),
+            ("lightning", L(heads=3, dim=10, vdim=14, decay=[0.5, 0.9, 0.995]), E(experts=5, top=3, ff=16, identity=1, groups=(2, 2))),
+            ("attention", A(**att, kv_from=0), E(experts=4, top=1, ff=20))])
+    if name == "dibizen-tiny-b":     # one stream; every head its own keys; no temperature, no cap, no groups, no identity outputs
+        return dibizen_config(vocab=300, width=80, streams=1, eps=1e-6, max_positions=400, logit_softcap=0.0, layers=[
+            ("lightning", L(heads=2, dim=40, vdim=24, decay=[0.97, 0.8]), E(experts=3, top=3, ff=32)),
+            ("attention", A(heads=5, kv_heads=5, dim=8, vdim=8), E(experts=8, top=2, ff=12, identity=0, groups=(4, 1))),
+            ("mamba1", M(inner=100, state=20, dt_rank=7, conv=2), E(experts=2, top=1, ff=40, identity=2, groups=(2, 1)))])
+    if name == "dibizen-tiny-c":     # head sizes the tensor-core attention takes (bfloat16); five taps; many states; shared keys twice
+        att = dict(heads=6, kv_heads=1, dim=32, vdim=64, scale=0.2, q_temp=(0.4, 50))
+        return dibizen_config(vocab=210, width=64, streams=2, max_positions=350, layers=[
+            ("mamba1", M(inner=96, state=80, dt_rank=3, conv=5), E(experts=7, top=2, ff=16, identity=1, groups=(4, 3))),
+            ("attention", A(**att), None),
+            ("attention", A(**att, kv_from=1), E(experts=4, top=2, ff=24, identity=4, groups=(2, 1))),
+            ("lightning", L(heads=4, dim=70, vdim=16, decay=[0.6, 0.9, 0.99, 0.999]), None),
+            ("attention", A(**att, kv_from=1), E(experts=3, top=2, ff=8, identity=1))])
+    return None
+
+
 def named_config(name: str) -> dict:
-    cfg = _kutirax_named(name.lower()) or _bobunex_named(name.lower())
+    cfg = _kutirax_named(name.lower()) or _bobunex_named(name.lower()) or _dibizen_named(name.lower())
     if cfg is not None:
         return cfg
     try:
         return qwen2_config(**NAMED_SIZES[name.lower()])
     except KeyError:
         known = sorted(NAMED_SIZES) + ["kutirax-tiny-a", "kutirax-tiny-b", "kutirax-tiny-c", "bobunex-tiny-a", "bobunex-tiny-b",
-                                       "bobunex-tiny-c", "bobunex-tiny-d"]
+                                       "bobunex-tiny-c", "bobunex-tiny-d", "dibizen-tiny-a", "dibizen-tiny-b", "dibizen-tiny-c"]
         raise ValueError(f"unknown size name {name!r}; known: {known}") from None
