@@ -19,7 +19,32 @@ namespace tmk {
 constexpr int kScanThreads = 128;
 constexpr int kScanTokens = 16;
 
-__device__ __forceinline__ float softplus32(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+// exp(x) to about one unit in the last place (1.05 at worst, a quarter on average): n = round(x / ln 2), r = x - n ln 2 with ln 2 in two pieces (the
+// high one has enough trailing zero bits for n * high to be exact), a degree-7 polynomial on |r| <= 0.347 (remainder below
+// 6e-9), then the exponent. Below -86 the result is 0. A decay is multiplied into a state once per token, so its error adds up
+// over a sequence: the 32-bit run, whose logits are compared to a few units of 32-bit rounding, takes this form; the
+// bfloat16 run takes expf (two units in the last place, on the special-function unit).
+__device__ __forceinline__ float exp_one_ulp(float x) {
+  if (x < -86.f) return 0.f;
+  x = fminf(x, 88.f);
+  const float n = rintf(x * 1.4426950408889634f);
+  float r = fmaf(n, -0.693145751953125f, x);
+  r = fmaf(n, -1.42860682030941723212e-6f, r);
+  float p = 1.f / 5040.f;
+  p = fmaf(p, r, 1.f / 720.f);
+  p = fmaf(p, r, 1.f / 120.f);
+  p = fmaf(p, r, 1.f / 24.f);
+  p = fmaf(p, r, 1.f / 6.f);
+  p = fmaf(p, r, 0.5f);
+  p = fmaf(p * r, r, r);                 // r + r^2 (1/2 + ...): the small part first, 1 last
+  p += 1.f;
+  return __int_as_float(__float_as_int(p) + (static_cast<int>(n) << 23));
+}
+
+template <typename T> __device__ __forceinline__ float exp_for(float x) { return expf(x); }
+template <> __device__ __forceinline__ float exp_for<float>(float x) { return exp_one_ulp(x); }
+
+template <typename T> __device__ __forceinline__ float softplus32(float v) { return v > 20.f ? v : log1pf(exp_for<T>(v)); }
 
 template <typename T, int NS, int L>
 __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(
@@ -52,7 +77,7 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(
   for (int j = 0; j < NS; ++j) {
     const int n = lane + L * j;
     const bool ok = live && n < N;
-    A[j] = ok ? -expf(A_log[(size_t)c * N + n]) : 0.f;
+    A[j] = ok ? -exp_for<T>(A_log[(size_t)c * N + n]) : 0.f;
     S[j] = ok ? S_row[n] : 0.f;
   }
   const float Dc = live ? Dv[c] : 0.f;
@@ -79,7 +104,7 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(
         const float* low = s_dbc + tt * P;
         float acc = 0.f;
         for (int r = 0; r < R; ++r) acc = fmaf(wr[r], low[r], acc);
-        dt = softplus32(acc + b_dt[c0 + cc]);
+        dt = softplus32<T>(acc + b_dt[c0 + cc]);
       }
       s_dt[i] = dt;
     }
@@ -94,7 +119,7 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(
       for (int j = 0; j < NS; ++j) {
         const int n = lane + L * j;
         if (n < N) {
-          S[j] = fmaf(expf(dt * A[j]), S[j], dx * Bv[n]);
+          S[j] = fmaf(exp_for<T>(dt * A[j]), S[j], dx * Bv[n]);
           y = fmaf(S[j], Cv[n], y);
         }
       }
