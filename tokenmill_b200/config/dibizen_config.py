@@ -3,7 +3,7 @@
     architecture    "Dibizen"
     vocab, width    vocabulary and residual width
     max_positions   rows of the learned position table
-    streams         copies of the residual stream (hyper-connections)
+    streams         copies of the residual stream (hyper-connections; absent: one plain stream without their tensors)
     norm.eps        eps of the RMS norms inside the mixers (the layers' own norms are Dynamic Tanh and have none)
     logit_softcap   cap of the logits (absent or 0: none)
     layers          one entry per layer: type ("attention" | "lightning" | "mamba1"), mixer (its sizes), mlp (null, or
@@ -40,6 +40,7 @@ class DibizenConfig:
     streams: int
     max_positions: int
     logit_softcap: float = 0.0
+    hyper_connections: bool = True      # False (no ``streams`` in the file): one stream, no read and write weights
     layers: list[DibizenLayer] = field(default_factory=list)
     eos_token_ids: list[int] = field(default_factory=list)
     architecture: str = "Dibizen"
@@ -128,6 +129,7 @@ class DibizenConfig:
         if cap < 0:
             raise ConfigError(f"config.json: logit_softcap must not be negative, got {cap!r}")
         return cls(vocab=_pos_int(raw["vocab"], "vocab"), width=_pos_int(raw["width"], "width"), eps=eps,
-                   streams=_pos_int(raw.get("streams", 1), "streams"),
+                   streams=_pos_int(raw["streams"], "streams") if raw.get("streams") is not None else 1,
+                   hyper_connections=raw.get("streams") is not None,
                    max_positions=_pos_int(raw["max_positions"], "max_positions"), logit_softcap=cap, layers=layers,
                    eos_token_ids=sorted(set(eos)))

@@ -52,7 +52,7 @@ def dibizen_spec(cfg: DibizenConfig) -> ModelSpec:
         layers.append(LayerSpec(prefix=f"l{i}", block="hyper_connections", mixer=mixer, feed_forward=ffn, mixer_norm=norm,
                                 feed_forward_norm=norm if ffn is not None else None, mixer_name="mix",
                                 feed_forward_name="mlp", mixer_norm_name="norm1", feed_forward_norm_name="norm2",
-                                block_params={"hidden_size": d, "streams": cfg.streams}))
+                                block_params={"hidden_size": d, "streams": cfg.streams, "learned": cfg.hyper_connections}))
         order.append(RunEntry(i, cache_of=cache_of))        # (one run per layer: a layer's number is its place in the order)
     return ModelSpec(architecture=cfg.architecture, hidden_size=d, vocab_size=cfg.vocab, embedding_name="embed",
                      layers=layers, run_order=order, final_norm=norm, final_norm_prefix="final.norm", lm_head_name="head",

@@ -222,9 +222,12 @@ class HyperConnectionBlock:
     wants_run_context = True
 
     def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, *, hidden_size: int, streams: int,
-                 names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
+                 learned: bool = True, names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
         if streams < 1:
             raise ValueError(f"a block has at least one residual stream, got {streams}")
+        if not learned and streams != 1:
+            raise ValueError("several residual streams need their learned read and write weights")
+        self.learned = bool(learned)     # False: one stream read and written as it is (no tensors): the plain block
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
         self.hidden_size, self.streams = hidden_size, int(streams)
@@ -241,14 +244,14 @@ class HyperConnectionBlock:
     def weight_specs(self):
         from .spec import WeightSpec
         s, n, out = self.streams, self.names, []
-        for i in self._sides():
+        for i in self._sides() if self.learned else []:
             out += [WeightSpec(n[f"in{i}"], (s,), dtype="float32", init=("normal", 0.2, 1.0 / s)),
                     WeightSpec(n[f"out{i}"], (s,), dtype="float32", init=("normal", 0.2, 1.0)),
                     WeightSpec(n[f"mix{i}"], (s, s), dtype="float32", init=("normal", 0.2, 1.0 / s))]
         return out
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
-        for i in self._sides():
+        for i in self._sides() if self.learned else []:
             self.w_in[i - 1] = tensors[self.names[f"in{i}"]]
             self.w_out[i - 1] = tensors[self.names[f"out{i}"]]
             self.w_mix[i - 1] = tensors[self.names[f"mix{i}"]]

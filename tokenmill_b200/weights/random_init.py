@@ -238,7 +238,7 @@ def _dibizen_named(name: str) -> dict | None:
             ("attention", A(heads=5, kv_heads=5, dim=8, vdim=8), E(experts=8, top=2, ff=12, identity=0, groups=(4, 1))),
             ("mamba1", M(inner=100, state=20, dt_rank=7, conv=2), E(experts=2, top=1, ff=40, identity=2, groups=(2, 1)))])
     if name == "dibizen-tiny-c":     # head sizes the tensor-core attention takes (bfloat16); five taps; many states; shared keys twice
-        att = dict(heads=6, kv_heads=1, dim=32, vdim=64, scale=0.2, q_temp=(0.4, 50))
+        att = dict(heads=8, kv_heads=2, dim=64, vdim=32, scale=0.2, q_temp=(0.4, 50))
         return dibizen_config(vocab=210, width=64, streams=2, max_positions=350, layers=[
             ("mamba1", M(inner=96, state=80, dt_rank=3, conv=5), E(experts=7, top=2, ff=16, identity=1, groups=(4, 3))),
             ("attention", A(**att), None),
