@@ -186,10 +186,12 @@ def test_stream_norm_kernel(dtype, streams):
 
 
 @pytest.mark.parametrize("inner,N,rank,taps", [(72, 12, 5, 3), (100, 20, 7, 2), (96, 80, 1, 5), (40, 200, 4, 4), (33, 1, 2, 1)])
+@pytest.mark.parametrize("slice_len", [0, 5, 16])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_convolution_and_selective_scan_under_cuts(dtype, inner, N, rank, taps):
+def test_convolution_and_selective_scan_under_cuts(dtype, inner, N, rank, taps, slice_len):
     """Two requests (slots 2 and 0 of 4) fed in steps of unequal sizes, single tokens among them: the convolution's
-    carried inputs and the scan's states against the plain functions over the whole sequences."""
+    carried inputs and the scan's states against the plain functions over the whole sequences. With a slice length the
+    scan runs its three passes over time slices (one request's last slice short, the other's slices fewer)."""
     from tokenmill_b200.kernels import ops
     torch.manual_seed(inner)
     n = 45
@@ -218,8 +220,14 @@ def test_convolution_and_selective_scan_under_cuts(dtype, inner, N, rank, taps):
         ops.conv_silu_state(rows, 0, inner, g(w_conv), g(b_conv), state, cu, seq_of, slots, xc)
         dbc = ops.linear32(xc, g(w_x).to(dtype))
         out = torch.empty(na + nb, inner, dtype=dtype, device=DEV)
+        sliced = {}
+        if slice_len:
+            slices = -(-max(na, nb) // slice_len)
+            sliced = dict(max_q_len=max(na, nb), slice_len=slice_len,
+                          slice_S=torch.full((2 * slices * inner * N,), float("nan"), device=DEV),
+                          slice_dt=torch.full((2 * slices * inner,), float("nan"), device=DEV))
         ops.selective_scan(xc, rows, inner, dbc, g(w_dt), g(b_dt), g(A_log), g(D), state, conv_len, cu, slots, out,
-                           n_seqs=2, rank=rank, N=N)
+                           n_seqs=2, rank=rank, N=N, **sliced)
         ref = torch.cat([want[0][fed[0]:fed[0] + na], want[1][fed[1]:fed[1] + nb]])
         _close(out.float(), ref, dtype, (fed, na, nb))
         fed = [fed[0] + na, fed[1] + nb]
@@ -227,9 +235,11 @@ def test_convolution_and_selective_scan_under_cuts(dtype, inner, N, rank, taps):
     assert float(state[:, conv_len + inner * N:].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("heads,d,dv", [(3, 10, 14), (1, 40, 72), (2, 64, 130), (2, 200, 24), (5, 1, 3)])
-def test_decay_memory_kernel_under_cuts(heads, d, dv):
-    """Per head S <- decay S + k v^T, o = S^T q, with silu on q, k and v, from strided 32-bit rows; slots 1 and 3 of 4."""
+@pytest.mark.parametrize("slice_len", [0, 5, 16])
+@pytest.mark.parametrize("heads,d,dv", [(3, 10, 14), (1, 40, 72), (2, 64, 130), (2, 200, 24), (5, 1, 3), (2, 300, 8)])
+def test_decay_memory_kernel_under_cuts(heads, d, dv, slice_len):
+    """Per head S <- decay S + k v^T, o = S^T q, with silu on q, k and v, from strided 32-bit rows; slots 1 and 3 of 4.
+    With a slice length the three passes over time slices run instead of one walk."""
     from tokenmill_b200.kernels import ops
     torch.manual_seed(d)
     n = 40
@@ -248,8 +258,14 @@ def test_decay_memory_kernel_under_cuts(heads, d, dv):
         rows = torch.cat([seqs[0][fed[0]:fed[0] + na], seqs[1][fed[1]:fed[1] + nb]]).to(DEV)
         cu, _, slots = _step_arrays([na, nb], [1, 3])
         y = torch.empty(na + nb, heads * dv, device=DEV)
+        sliced = {}
+        if slice_len:
+            slices = -(-max(na, nb) // slice_len)
+            sliced = dict(max_q_len=max(na, nb), slice_len=slice_len,
+                          slice_S=torch.full((2 * slices * heads * d * dv,), float("nan"), device=DEV))
         ops.decay_memory(rows[:, 5:], q_col=col["q"], k_col=col["k"], v_col=col["v"], activation="silu", decay=decay.to(DEV),
-                         state=state, state_off=8, cu_q=cu, state_slots=slots, y=y, n_seqs=2, heads=heads, dim=d, vdim=dv)
+                         state=state, state_off=8, cu_q=cu, state_slots=slots, y=y, n_seqs=2, heads=heads, dim=d, vdim=dv,
+                         **sliced)
         ref = torch.cat([want[0][fed[0]:fed[0] + na], want[1][fed[1]:fed[1] + nb]])
         _close(y, ref, torch.float32, (fed, na, nb))
         fed = [fed[0] + na, fed[1] + nb]

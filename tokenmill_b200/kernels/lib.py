@@ -97,8 +97,11 @@ _SIGNATURES: dict[str, list] = {
     "tm_add_scaled_rows": [_I, _P, _P, _P, _I, _I, _P],
     "tm_stream_norm": [_I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _P, _P, _P, _F, _P, _I, _P],
     "tm_softcap": [_P, _LL, _F, _P],
-    "tm_selective_scan": [_I, _P, _I, _P, _LL, _I, _P, _LL, _I, _I, _P, _P, _P, _P, _P, _LL, _LL, _P, _P, _P, _I, _P],
-    "tm_decay_memory": [_P, _LL, _I, _I, _I, _I, _P, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tm_selective_scan": [_I, _P, _I, _P, _LL, _I, _P, _LL, _I, _I, _P, _P, _P, _P, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I,
+                          _P, _P, _P],
+    "tm_selective_pass_states": [_I, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "tm_decay_memory": [_P, _LL, _I, _I, _I, _I, _P, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "tm_decay_pass_states": [_P, _LL, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "tm_matrix_memory": [_P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P, _LL, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P,
                          _LL, _I, _P],
     "tm_matrix_memory_pass_states": [_P, _LL, _LL, _P, _P, _I, _I, _I, _I, _I, _P, _LL, _P],
@@ -121,8 +124,8 @@ _BY_FILE = {
     "sink_attention_mma_bf16.cu": {"tm_sink_attention_mma_bf16"},
     "matrix_memory.cu": {"tm_matrix_memory", "tm_matrix_memory_pass_states"},
     "stream_norm.cu": {"tm_stream_norm", "tm_softcap"},
-    "selective_scan.cu": {"tm_selective_scan"},
-    "decay_memory.cu": {"tm_decay_memory"},
+    "selective_scan.cu": {"tm_selective_scan", "tm_selective_pass_states"},
+    "decay_memory.cu": {"tm_decay_memory", "tm_decay_pass_states"},
 }
 _BOTH = {"tm_gemm_f32_nt"}            # in every library
 _GROUPS_OF: dict[str, list[str]] = {}     # entry point -> the libraries that hold it, in the order of kernels/build.py

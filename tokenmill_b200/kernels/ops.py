@@ -1345,20 +1345,40 @@ def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
 
 def selective_scan(x: torch.Tensor, z: torch.Tensor, z_col: int, dbc: torch.Tensor, w_dt: torch.Tensor, b_dt: torch.Tensor,
                    A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, state_off: int, cu_q: torch.Tensor,
-                   state_slots: torch.Tensor, out: torch.Tensor, *, n_seqs: int, rank: int, N: int) -> torch.Tensor:
+                   state_slots: torch.Tensor, out: torch.Tensor, *, n_seqs: int, rank: int, N: int, max_q_len: int = 0,
+                   slice_len: int = 0, slice_S: torch.Tensor | None = None, slice_dt: torch.Tensor | None = None) -> torch.Tensor:
     """x [T, inner] (convolved, activated); z: the gate's pre-activations at columns z_col .. z_col + inner of a matrix in x's
     dtype; dbc [T, rank + 2 N] float32 = [low | B | C]; w_dt [inner, rank], b_dt [inner], A_log [inner, N], D [inner] float32;
-    a request's states [inner, N] live ``state_off`` floats into its slot. out [T, inner] = (scan + D x) silu(z)."""
+    a request's states [inner, N] live ``state_off`` floats into its slot. out [T, inner] = (scan + D x) silu(z).
+    ``slice_len`` > 0: three passes over time slices of that many tokens (for long prompt portions), through ``slice_S``
+    (n_seqs * slices * inner * N float32) and ``slice_dt`` (n_seqs * slices * inner float32), slices =
+    ceil(max_q_len / slice_len)."""
     T, inner = x.shape
     if out.shape != x.shape or dbc.shape != (T, rank + 2 * N) or z.shape[0] != T or z_col + inner > z.shape[1] or \
             tuple(w_dt.shape) != (inner, rank) or tuple(A_log.shape) != (inner, N) or b_dt.numel() != inner or D.numel() != inner or \
             state.shape[1] < state_off + inner * N or z.dtype != x.dtype or z.stride(1) != 1:
         raise lib.KernelError("selective_scan: shapes do not fit")
-    lib.call("tm_selective_scan", _code(x.dtype), _req(x, "x"), inner, z.data_ptr(), z.stride(0), int(z_col),
-             _req(dbc, "dbc", torch.float32), dbc.stride(0), int(rank), int(N), _req(w_dt, "w_dt", torch.float32),
-             _req(b_dt, "b_dt", torch.float32), _req(A_log, "A_log", torch.float32), _req(D, "D", torch.float32),
-             _req(state, "state", torch.float32), state.stride(0), int(state_off), _req(cu_q, "cu_q", torch.int32),
-             _req(state_slots, "state_slots", torch.int32), _req(out, "out", x.dtype), int(n_seqs), _stream())
+
+    def scan(mode, max_slices):
+        lib.call("tm_selective_scan", _code(x.dtype), _req(x, "x"), inner, z.data_ptr(), z.stride(0), int(z_col),
+                 _req(dbc, "dbc", torch.float32), dbc.stride(0), int(rank), int(N), _req(w_dt, "w_dt", torch.float32),
+                 _req(b_dt, "b_dt", torch.float32), _req(A_log, "A_log", torch.float32), _req(D, "D", torch.float32),
+                 _req(state, "state", torch.float32), state.stride(0), int(state_off), _req(cu_q, "cu_q", torch.int32),
+                 _req(state_slots, "state_slots", torch.int32), _req(out, "out", x.dtype), int(n_seqs), mode, int(slice_len),
+                 max_slices, _opt(slice_S, "slice_S", torch.float32), _opt(slice_dt, "slice_dt", torch.float32), _stream())
+
+    if slice_len <= 0:
+        scan(0, 1)
+        return out
+    slices = -(-int(max_q_len) // int(slice_len))
+    if slices < 1 or slice_S is None or slice_dt is None or slice_S.numel() < n_seqs * slices * inner * N or \
+            slice_dt.numel() < n_seqs * slices * inner:
+        raise lib.KernelError("selective_scan: scratch for the time slices is missing or too small")
+    scan(1, slices)
+    lib.call("tm_selective_pass_states", _code(x.dtype), state.data_ptr(), state.stride(0), int(state_off), cu_q.data_ptr(),
+             state_slots.data_ptr(), A_log.data_ptr(), slice_S.data_ptr(), slice_dt.data_ptr(), int(n_seqs), inner, int(N),
+             int(slice_len), slices, _stream())
+    scan(2, slices)
     return out
 
 
@@ -1367,17 +1387,34 @@ DECAY_ACTIVATIONS = {None: 0, "none": 0, "silu": 1}
 
 def decay_memory(proj: torch.Tensor, *, q_col: int, k_col: int, v_col: int, activation: str | None, decay: torch.Tensor,
                  state: torch.Tensor, state_off: int, cu_q: torch.Tensor, state_slots: torch.Tensor, y: torch.Tensor,
-                 n_seqs: int, heads: int, dim: int, vdim: int) -> torch.Tensor:
+                 n_seqs: int, heads: int, dim: int, vdim: int, max_q_len: int = 0, slice_len: int = 0,
+                 slice_S: torch.Tensor | None = None) -> torch.Tensor:
     """proj [T, P] float32 (rows may be strided) with q, k (heads x dim) and v (heads x vdim) at the given columns, each
     through ``activation``; per head S <- decay S + k v^T, y = S^T q; a request's memories [heads, dim, vdim] live
-    ``state_off`` floats into its slot; y [T, heads * vdim] float32."""
+    ``state_off`` floats into its slot; y [T, heads * vdim] float32. ``slice_len`` > 0: three passes over time slices of
+    that many tokens (for long prompt portions), through ``slice_S`` (n_seqs * slices * heads * dim * vdim float32),
+    slices = ceil(max_q_len / slice_len)."""
     T = proj.shape[0]
     if proj.dtype != torch.float32 or proj.stride(1) != 1 or y.shape != (T, heads * vdim) or decay.numel() != heads or \
             max(q_col, k_col) + heads * dim > proj.shape[1] or v_col + heads * vdim > proj.shape[1] or \
             state.shape[1] < state_off + heads * dim * vdim or activation not in DECAY_ACTIVATIONS:
         raise lib.KernelError("decay_memory: shapes do not fit")
-    lib.call("tm_decay_memory", proj.data_ptr(), proj.stride(0), int(q_col), int(k_col), int(v_col), DECAY_ACTIVATIONS[activation],
-             _req(decay, "decay", torch.float32), _req(state, "state", torch.float32), state.stride(0), int(state_off),
-             _req(cu_q, "cu_q", torch.int32), _req(state_slots, "state_slots", torch.int32), _req(y, "y", torch.float32),
-             int(n_seqs), heads, dim, vdim, _stream())
+
+    def walk(mode, max_slices):
+        lib.call("tm_decay_memory", proj.data_ptr(), proj.stride(0), int(q_col), int(k_col), int(v_col),
+                 DECAY_ACTIVATIONS[activation], _req(decay, "decay", torch.float32), _req(state, "state", torch.float32),
+                 state.stride(0), int(state_off), _req(cu_q, "cu_q", torch.int32), _req(state_slots, "state_slots", torch.int32),
+                 _req(y, "y", torch.float32), int(n_seqs), heads, dim, vdim, mode, int(slice_len), max_slices,
+                 _opt(slice_S, "slice_S", torch.float32), _stream())
+
+    if slice_len <= 0:
+        walk(0, 1)
+        return y
+    slices = -(-int(max_q_len) // int(slice_len))
+    if slices < 1 or slice_S is None or slice_S.numel() < n_seqs * slices * heads * dim * vdim:
+        raise lib.KernelError("decay_memory: scratch for the time slices is missing or too small")
+    walk(1, slices)
+    lib.call("tm_decay_pass_states", state.data_ptr(), state.stride(0), int(state_off), cu_q.data_ptr(), state_slots.data_ptr(),
+             decay.data_ptr(), slice_S.data_ptr(), int(n_seqs), heads, dim, vdim, int(slice_len), slices, _stream())
+    walk(2, slices)
     return y

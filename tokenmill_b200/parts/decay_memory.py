@@ -7,7 +7,10 @@ with one constant ``decay_h`` per head and no other scale. The heads side by sid
 square over all heads x dv numbers, a plain weight), multiplied by sigmoid(W_g h), and projected by W_o. The memory, the
 products and the norm are 32-bit in both run dtypes; the projections' product keeps its 32-bit accumulator. Per request
 the mixer keeps S [heads, d, dv] in ONE state slot of 32-bit floats, zero for a new request; prompt portions and single
-decoded tokens run the same kernel, which walks a request's tokens in order whatever the cut.
+decoded tokens run the same kernel, which walks a request's tokens in order whatever the cut. A step whose longest
+portion has ``SLICED_FROM`` tokens runs three passes over time slices instead (the slices' own memories side by side,
+then their start memories one after the other, then the slices again with the results): the same sums in another
+order.
 """
 
 from __future__ import annotations
@@ -18,6 +21,11 @@ from ..kernels import ops
 from ..registry import register_mixer
 from .base import LayerCache, StepInputs
 from .spec import StateNeed, WeightSpec
+
+
+SLICED_FROM = 256               # a step whose longest portion has this many tokens runs over time slices
+SLICE_LEN = 128
+SLICE_SCRATCH_LIMIT = 1 << 28    # bytes of scratch the slices may take; beyond it a step walks each request in one piece
 
 
 class DecayMemoryMixer:
@@ -65,9 +73,15 @@ class DecayMemoryMixer:
         T, dev, c = x.shape[0], x.device, self.col
         proj = ops.linear32(x, self.w_in)                                       # [T, q | k | v | g] float32
         y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
+        sliced = {}
+        if step.max_q_len >= SLICED_FROM and step.workspace is not None:
+            need = -(-step.max_q_len // SLICE_LEN) * step.n_seqs * self.nh * self.d * self.dv
+            if need * 4 <= SLICE_SCRATCH_LIMIT:
+                sliced = dict(max_q_len=step.max_q_len, slice_len=SLICE_LEN,
+                              slice_S=step.workspace.get("decay_slice_memories", need, torch.float32))
         ops.decay_memory(proj, q_col=c["q"], k_col=c["k"], v_col=c["v"], activation=self.activation, decay=self.decay,
                          state=cache.state, state_off=0, cu_q=step.cu_q, state_slots=step.state_slots, y=y,
-                         n_seqs=step.n_seqs, heads=self.nh, dim=self.d, vdim=self.dv)
+                         n_seqs=step.n_seqs, heads=self.nh, dim=self.d, vdim=self.dv, **sliced)
         gated = torch.empty((T, self.inner), dtype=self.dtype, device=dev)
         # one "head" of all the numbers: the heads are normed together
         ops.head_norm_gate(y, proj[:, c["g"]:c["g"] + self.inner], self.g, self.eps, 1, gated)

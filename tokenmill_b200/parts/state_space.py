@@ -23,6 +23,8 @@ from .spec import StateNeed, WeightSpec
 
 SLICED_FROM = 256       # a step whose longest portion has this many tokens runs the recurrence over time slices
 SLICE_LEN = 128
+SLICE_SCRATCH_LIMIT = 1 << 28    # bytes of scratch the selective scan's slices may take; beyond it a step walks each
+                                 # request in one piece
 VECTOR_CONV_FROM = 16   # steps whose longest portion is shorter are mostly rows that own a slot: a thread per channel
                         # (8 decoded tokens at 2,560 channels: 5 us against 14 with eight channels a thread)
 
@@ -111,7 +113,8 @@ class SelectiveScanMixer:
 
     Per request the mixer keeps, in ONE state slot of 32-bit floats: the last ``taps - 1`` inputs of the convolution
     [(taps - 1), inner], then S [inner, N]; zero for a new request. The recurrence walks a request's tokens in order
-    whatever the cut."""
+    whatever the cut; a step whose longest portion has ``SLICED_FROM`` tokens runs three passes over time slices instead
+    (a slice's decays multiply to exp(A times the sum of its step sizes)): the same sums in another order."""
 
     def __init__(self, *, hidden_size: int, inner: int, state_size: int, dt_rank: int, conv_taps: int,
                  names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
@@ -163,8 +166,15 @@ class SelectiveScanMixer:
                             step.state_slots, xc, weight_t=self.w_conv_t if step.max_q_len >= VECTOR_CONV_FROM else None)
         dbc = ops.linear32(xc, self.w_x)                                      # [T, low | B | C] float32
         gated = torch.empty((T, self.inner), dtype=self.dtype, device=dev)
+        sliced = {}
+        if step.max_q_len >= SLICED_FROM and step.workspace is not None:
+            slices = -(-step.max_q_len // SLICE_LEN) * step.n_seqs
+            if slices * self.inner * (self.N + 1) * 4 <= SLICE_SCRATCH_LIMIT:
+                sliced = dict(max_q_len=step.max_q_len, slice_len=SLICE_LEN,
+                              slice_S=step.workspace.get("scan_slice_states", slices * self.inner * self.N, torch.float32),
+                              slice_dt=step.workspace.get("scan_slice_steps", slices * self.inner, torch.float32))
         ops.selective_scan(xc, proj, self.inner, dbc, self.w_dt, self.b_dt, self.A_log, self.D, cache.state, self.conv_len,
-                           step.cu_q, step.state_slots, gated, n_seqs=step.n_seqs, rank=self.rank, N=self.N)
+                           step.cu_q, step.state_slots, gated, n_seqs=step.n_seqs, rank=self.rank, N=self.N, **sliced)
         return ops.linear(gated, self.w_o)
 
 
