@@ -98,7 +98,7 @@ def test_cache_layout_shared_pages_and_state_slots():
     layout = model.cache_layout()
     assert [(g.need.head_dim, g.need.window, g.need.planes, g.entries) for g in layout.groups] == [(2 * (12 + 20), None, 1, [0])]
     assert layout.entry_group[3] == layout.entry_group[0] and set(layout.entry_group) == {0, 3}
-    assert layout.entry_state[1].shape == ((3 - 1) * 72 + 72 * 12,) and layout.entry_state[2].shape == (3 * 10 * 14,)
+    assert layout.entry_state[1].shape == ((3 - 1) * 72 + 72 * 12,) and layout.entry_state[2].shape == (3 * 14 * 16,)       # 10 rows padded to 16
     assert set(layout.entry_state) == {1, 2} and not layout.block_state
     _, c = _model("dibizen-tiny-c")
     layout = c.cache_layout()

@@ -144,14 +144,15 @@ def _close(got, ref, dtype, what=""):
 
 # --- mechanisms alone -------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("streams", [1, 3, 4])
+@pytest.mark.parametrize("streams,width", [(1, 52), (2, 52), (3, 52), (4, 52), (5, 52), (2, 50), (4, 1030), (6, 37)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_stream_norm_kernel(dtype, streams):
+def test_stream_norm_kernel(dtype, streams, width):
     """Start from embedding rows and position vectors, take in a result of two pieces through a mix, read through the
-    read weights, and at the end norm the plain sum of a few rows without touching the residual."""
+    read weights, and at the end norm the plain sum of a few rows without touching the residual. Up to four streams of a
+    width that is a multiple of four take four numbers per access; the rest one."""
     from tokenmill_b200.kernels import ops
     torch.manual_seed(streams)
-    T, H, S = 9, 52, streams
+    T, H, S = 9, width, streams
     table, pos = torch.randn(30, H).to(dtype), torch.randn(40, H).to(dtype)
     ids, positions = torch.randint(0, 30, (T,)), torch.randint(0, 40, (T,))
     w, b, alpha = 1 + 0.1 * torch.randn(H), 0.1 * torch.randn(H), torch.tensor([0.7])
@@ -252,7 +253,8 @@ def test_decay_memory_kernel_under_cuts(heads, d, dv, slice_len):
         p = pd.silu(s.double()[:, 5:])
         want.append(pd.decay_memory(p[:, :heads * d].view(n, heads, d), p[:, col["k"]:col["v"]].view(n, heads, d),
                                     p[:, col["v"]:].reshape(n, heads, dv), [float(a) for a in decay]).reshape(n, heads * dv))
-    state = torch.zeros(4, 8 + heads * d * dv, device=DEV)
+    floats = ops.decay_memory_state_floats(heads, d, dv)
+    state = torch.zeros(4, 8 + floats, device=DEV)
     fed = [0, 0]
     for na, nb in ((1, 17), (20, 1), (2, 1), (17, 21)):
         rows = torch.cat([seqs[0][fed[0]:fed[0] + na], seqs[1][fed[1]:fed[1] + nb]]).to(DEV)
@@ -262,7 +264,7 @@ def test_decay_memory_kernel_under_cuts(heads, d, dv, slice_len):
         if slice_len:
             slices = -(-max(na, nb) // slice_len)
             sliced = dict(max_q_len=max(na, nb), slice_len=slice_len,
-                          slice_S=torch.full((2 * slices * heads * d * dv,), float("nan"), device=DEV))
+                          slice_S=torch.full((2 * slices * floats,), float("nan"), device=DEV))
         ops.decay_memory(rows[:, 5:], q_col=col["q"], k_col=col["k"], v_col=col["v"], activation="silu", decay=decay.to(DEV),
                          state=state, state_off=8, cu_q=cu, state_slots=slots, y=y, n_seqs=2, heads=heads, dim=d, vdim=dv,
                          **sliced)
@@ -270,6 +272,21 @@ def test_decay_memory_kernel_under_cuts(heads, d, dv, slice_len):
         _close(y, ref, torch.float32, (fed, na, nb))
         fed = [fed[0] + na, fed[1] + nb]
     assert float(state[0].abs().max()) == 0.0 and float(state[:, :8].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,dv", [(1, 600), (2, 512), (1, 1030)])
+def test_norm_and_gate_over_wide_heads(heads, dv, dtype):
+    """Heads normed together are one head of many numbers: a block per row then, with a sum over its warps."""
+    from tokenmill_b200.kernels import ops
+    torch.manual_seed(dv)
+    n = 9
+    y, wide, w = torch.randn(n, heads * dv) * 4, torch.randn(n, heads * dv + 4), torch.randn(heads * dv)
+    out = ops.head_norm_gate(y.to(DEV), wide.to(DEV)[:, 4:], w.to(DEV), 1e-5, heads,
+                             torch.empty(n, heads * dv, dtype=dtype, device=DEV))
+    yd = y.double().view(n, heads, dv)
+    ref = (yd / (yd.pow(2).mean(-1, keepdim=True) + 1e-5).sqrt()).reshape(n, -1) * w.double() * torch.sigmoid(wide.double()[:, 4:])
+    _close(out.float(), ref, dtype, (heads, dv))
 
 
 @pytest.mark.parametrize("experts,identity,top,groups,keep", [(6, 2, 2, 4, 2), (5, 1, 3, 2, 2), (4, 0, 1, 1, 1), (8, 0, 2, 4, 1),

@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(256) norm_pair_mean_kernel(const T* __restrict
     out[row + i] = from_float<T>(0.5f * (to_float(a[row + i]) * ra * wa[i] + to_float(b[row + i]) * rb * wb[i]));
 }
 
-// One warp per (row, head).
+// One warp per (row, head); heads of 512 numbers and more take head_norm_gate_block_kernel.
 template <typename T>
 __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ den,
                                                              const float* __restrict__ gate,
@@ -268,6 +268,31 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __rest
     const float z = gate[(size_t)t * gate_stride + c];
     out[(size_t)pair * dv + i] = from_float<T>(src[i] / dn * rstd * w[c] / (1.0f + expf(-z)));
   }
+}
+
+// One block per (row, head), for heads of many numbers (heads normed together count as one head).
+template <typename T>
+__global__ void __launch_bounds__(256) head_norm_gate_block_kernel(const float* __restrict__ y, const float* __restrict__ den,
+                                                                   const float* __restrict__ gate, long long gate_stride,
+                                                                   const float* __restrict__ w, float eps, T* __restrict__ out,
+                                                                   int heads, int dv) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long pair = blockIdx.x;
+  const long long t = pair / heads;
+  const int hd = (int)(pair - t * heads);
+  const float* src = y + (size_t)pair * dv;
+  const float* g = gate + (size_t)t * gate_stride + (size_t)hd * dv;
+  const float dn = den ? den[pair] : 1.f;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dv; i += blockDim.x) {
+    const float o = src[i] / dn;
+    ss += o * o;
+  }
+  const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)dv + eps);
+  for (int i = threadIdx.x; i < dv; i += blockDim.x)
+    out[(size_t)pair * dv + i] = from_float<T>(src[i] / dn * rstd * w[hd * dv + i] / (1.0f + expf(-g[i])));
 }
 
 }  // namespace tmk
@@ -345,6 +370,10 @@ extern "C" int tm_head_norm_gate(int dtype, const float* y, const float* den, co
                                  float eps, void* out, int T_rows, int heads, int dv, cudaStream_t stream) {
   if (T_rows <= 0) return 0;
   const long long pairs = (long long)T_rows * heads;
+  if (dv >= 512) {
+    TM_BY_DTYPE(dtype, return launch_pdl(head_norm_gate_block_kernel<T>, dim3((unsigned)pairs), dim3(256), 0, stream, y, den, gate,
+                                         gate_stride, w, eps, (T*)out, heads, dv))
+  }
   TM_BY_DTYPE(dtype, return launch_pdl(head_norm_gate_kernel<T>, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, stream, y,
                                        den, gate, gate_stride, w, eps, (T*)out, heads, dv, pairs))
 }

@@ -18,7 +18,19 @@ namespace tmk {
 
 constexpr int kMaxStreams = 8;
 
-template <typename T>
+// W consecutive elements per access (W = 4: 16 bytes of float, 8 of bfloat16; the pointer must be aligned so).
+template <int W, typename T> __device__ __forceinline__ void ldw(const T* p, float (&v)[W]) {
+  if constexpr (W == 4) load4(p, v);
+  else v[0] = to_float(p[0]);
+}
+template <int W, typename T> __device__ __forceinline__ void stw(T* p, const float (&v)[W]) {
+  if constexpr (W == 4) store4(p, v);
+  else p[0] = from_float<T>(v[0]);
+}
+
+// SC: the number of streams when it is 1 to 4 (loops unrolled without tests), 0 for any number up to kMaxStreams.
+// W: elements per thread and access in the first pass over the row.
+template <typename T, int SC, int W>
 __global__ void __launch_bounds__(256) stream_norm_kernel(
     float* __restrict__ resid, int S, int H, const int* __restrict__ ids, const T* __restrict__ table,
     const int* __restrict__ positions, const T* __restrict__ pos_table, const T* __restrict__ branch,
@@ -26,6 +38,7 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(
     const float* __restrict__ mix, const float* __restrict__ out_w, const float* __restrict__ in_w,
     const int* __restrict__ rows, int mode, const float* __restrict__ alpha_p, const float* __restrict__ w,
     const float* __restrict__ b, float eps, T* __restrict__ out) {
+  constexpr int NS = SC ? SC : kMaxStreams;
   __shared__ float red[32];
   __shared__ float coef[kMaxStreams * kMaxStreams + 2 * kMaxStreams];
   pdl_launch_dependents();
@@ -51,50 +64,82 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(
   T* o_row = out + (size_t)r * H;
 
   float sq = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float xs[kMaxStreams];
+  for (int i = threadIdx.x * W; i < H; i += blockDim.x * W) {
+    float xs[NS][W];
     if (start) {
-      float v = to_float(e_row[i]);
-      if (p_row) v += to_float(p_row[i]);
+      float v[W];
+      ldw<W>(e_row + i, v);
+      if (p_row) {
+        float pv[W];
+        ldw<W>(p_row + i, pv);
 #pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s)
-        if (s < S) xs[s] = v;
-    } else {
-#pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s)
-        if (s < S) xs[s] = x[(size_t)s * H + i];
-    }
-    if (takes) {
-      float y = branch ? to_float(branch[(size_t)t * H + i]) : 0.f;
-      if (branch2) y = fmaf(rs, to_float(branch2[(size_t)t * H + i]), y);
-      float nx[kMaxStreams];
-#pragma unroll
-      for (int to = 0; to < kMaxStreams; ++to) {
-        if (to >= S) continue;
-        float acc = 0.f;
-#pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s)
-          if (s < S) acc = fmaf(m_s[s * S + to], xs[s], acc);
-        nx[to] = fmaf(o_s[to], y, acc);
+        for (int e = 0; e < W; ++e) v[e] += pv[e];
       }
 #pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s)
-        if (s < S) xs[s] = nx[s];
+      for (int s = 0; s < NS; ++s)
+#pragma unroll
+        for (int e = 0; e < W; ++e) xs[s][e] = v[e];
+    } else {
+#pragma unroll
+      for (int s = 0; s < NS; ++s)
+        if (SC || s < S) ldw<W>(x + (size_t)s * H + i, xs[s]);
+    }
+    if (takes) {
+      float y[W];
+#pragma unroll
+      for (int e = 0; e < W; ++e) y[e] = 0.f;
+      if (branch) ldw<W>(branch + (size_t)t * H + i, y);
+      if (branch2) {
+        float y2[W];
+        ldw<W>(branch2 + (size_t)t * H + i, y2);
+#pragma unroll
+        for (int e = 0; e < W; ++e) y[e] = fmaf(rs, y2[e], y[e]);
+      }
+      float nx[NS][W];
+#pragma unroll
+      for (int to = 0; to < NS; ++to) {
+        if (!SC && to >= S) continue;
+#pragma unroll
+        for (int e = 0; e < W; ++e) {
+          float acc = 0.f;
+#pragma unroll
+          for (int s = 0; s < NS; ++s)
+            if (SC || s < S) acc = fmaf(m_s[s * S + to], xs[s][e], acc);
+          nx[to][e] = fmaf(o_s[to], y[e], acc);
+        }
+      }
+#pragma unroll
+      for (int s = 0; s < NS; ++s)
+        if (SC || s < S) {
+#pragma unroll
+          for (int e = 0; e < W; ++e) xs[s][e] = nx[s][e];
+        }
     }
     if (!rows && (start || takes)) {
 #pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s)
-        if (s < S) x[(size_t)s * H + i] = xs[s];
+      for (int s = 0; s < NS; ++s)
+        if (SC || s < S) stw<W>(x + (size_t)s * H + i, xs[s]);
     }
-    float u = 0.f;
+    float u[W];
 #pragma unroll
-    for (int s = 0; s < kMaxStreams; ++s)
-      if (s < S) u = fmaf(i_s[s], xs[s], u);
+    for (int e = 0; e < W; ++e) {
+      u[e] = 0.f;
+#pragma unroll
+      for (int s = 0; s < NS; ++s)
+        if (SC || s < S) u[e] = fmaf(i_s[s], xs[s][e], u[e]);
+    }
     if (mode == 0) {
-      o_row[i] = from_float<T>(fmaf(tanhf(alpha * u), w[i], b ? b[i] : 0.f));
+      float wv[W], o[W];
+      ldw<W>(w + i, wv);
+#pragma unroll
+      for (int e = 0; e < W; ++e) o[e] = 0.f;
+      if (b) ldw<W>(b + i, o);
+#pragma unroll
+      for (int e = 0; e < W; ++e) o[e] = fmaf(tanhf(alpha * u[e]), wv[e], o[e]);
+      stw<W>(o_row + i, o);
     } else {
-      sq = fmaf(u, u, sq);
-      // the RMS form needs the whole row's sum first: u is computed again below
+#pragma unroll
+      for (int e = 0; e < W; ++e) sq = fmaf(u[e], u[e], sq);       // the RMS form needs the whole row's sum first: u is computed again below
     }
   }
   if (mode == 0) return;
@@ -142,9 +187,22 @@ int launch_stream_norm(float* resid, int S, int H, const int* ids, const void* t
                        const void* branch, const void* branch2, const float* row_scale, long long row_scale_stride,
                        const float* mix, const float* out_w, const float* in_w, const int* rows, int mode, const float* alpha,
                        const float* w, const float* b, float eps, void* out, int n_rows, cudaStream_t stream) {
-  return launch_pdl(stream_norm_kernel<T>, dim3(n_rows), dim3(256), 0, stream, resid, S, H, ids, (const T*)table, positions,
-                    (const T*)pos_table, (const T*)branch, (const T*)branch2, row_scale, row_scale_stride, mix, out_w, in_w, rows,
-                    mode, alpha, w, b, eps, (T*)out);
+  // four elements per access where every row starts on 16 bytes
+  const uintptr_t all = (uintptr_t)resid | (uintptr_t)table | (uintptr_t)pos_table | (uintptr_t)branch | (uintptr_t)branch2 |
+                        (uintptr_t)w | (uintptr_t)b | (uintptr_t)out;
+  const bool wide = !(H & 3) && !(all & 15);
+#define TM_STREAMS(SC_, W_)                                                                                                  \
+  return launch_pdl(stream_norm_kernel<T, SC_, W_>, dim3(n_rows), dim3(256), 0, stream, resid, S, H, ids, (const T*)table,   \
+                    positions, (const T*)pos_table, (const T*)branch, (const T*)branch2, row_scale, row_scale_stride, mix,   \
+                    out_w, in_w, rows, mode, alpha, w, b, eps, (T*)out)
+  if (wide) {
+    if (S == 1) TM_STREAMS(1, 4);
+    if (S == 2) TM_STREAMS(2, 4);
+    if (S == 3) TM_STREAMS(3, 4);
+    if (S == 4) TM_STREAMS(4, 4);
+  }
+  TM_STREAMS(0, 1);
+#undef TM_STREAMS
 }
 
 }  // namespace tmk

@@ -102,6 +102,7 @@ _SIGNATURES: dict[str, list] = {
     "tm_selective_pass_states": [_I, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "tm_decay_memory": [_P, _LL, _I, _I, _I, _I, _P, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "tm_decay_pass_states": [_P, _LL, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "tm_decay_activate": [_P, _LL, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "tm_matrix_memory": [_P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P, _LL, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P,
                          _LL, _I, _P],
     "tm_matrix_memory_pass_states": [_P, _LL, _LL, _P, _P, _I, _I, _I, _I, _I, _P, _LL, _P],
@@ -125,7 +126,7 @@ _BY_FILE = {
     "matrix_memory.cu": {"tm_matrix_memory", "tm_matrix_memory_pass_states"},
     "stream_norm.cu": {"tm_stream_norm", "tm_softcap"},
     "selective_scan.cu": {"tm_selective_scan", "tm_selective_pass_states"},
-    "decay_memory.cu": {"tm_decay_memory", "tm_decay_pass_states"},
+    "decay_memory.cu": {"tm_decay_memory", "tm_decay_pass_states", "tm_decay_activate"},
 }
 _BOTH = {"tm_gemm_f32_nt"}            # in every library
 _GROUPS_OF: dict[str, list[str]] = {}     # entry point -> the libraries that hold it, in the order of kernels/build.py

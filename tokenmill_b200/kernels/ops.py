@@ -1385,36 +1385,53 @@ def selective_scan(x: torch.Tensor, z: torch.Tensor, z_col: int, dbc: torch.Tens
 DECAY_ACTIVATIONS = {None: 0, "none": 0, "silu": 1}
 
 
+def decay_memory_state_floats(heads: int, dim: int, vdim: int) -> int:
+    """Floats of a request's memories as the kernel lays them out: [heads][vdim][d_pad], a column's rows side by side, 16
+    rows on each of the power-of-two lanes that share a column (csrc/decay_memory.cu)."""
+    parts = 1
+    while parts * 16 < dim:
+        parts *= 2
+    return heads * vdim * parts * 16
+
+
 def decay_memory(proj: torch.Tensor, *, q_col: int, k_col: int, v_col: int, activation: str | None, decay: torch.Tensor,
                  state: torch.Tensor, state_off: int, cu_q: torch.Tensor, state_slots: torch.Tensor, y: torch.Tensor,
                  n_seqs: int, heads: int, dim: int, vdim: int, max_q_len: int = 0, slice_len: int = 0,
                  slice_S: torch.Tensor | None = None) -> torch.Tensor:
     """proj [T, P] float32 (rows may be strided) with q, k (heads x dim) and v (heads x vdim) at the given columns, each
-    through ``activation``; per head S <- decay S + k v^T, y = S^T q; a request's memories [heads, dim, vdim] live
-    ``state_off`` floats into its slot; y [T, heads * vdim] float32. ``slice_len`` > 0: three passes over time slices of
-    that many tokens (for long prompt portions), through ``slice_S`` (n_seqs * slices * heads * dim * vdim float32),
-    slices = ceil(max_q_len / slice_len)."""
+    through ``activation``; per head S <- decay S + k v^T, y = S^T q; a request's memories
+    (``decay_memory_state_floats`` floats) live ``state_off`` floats into its slot; y [T, heads * vdim] float32.
+    ``slice_len`` > 0: three passes over time slices of that many tokens (for long prompt portions), through ``slice_S``
+    (n_seqs * slices memories, float32), slices = ceil(max_q_len / slice_len); this run applies the activation to the q,
+    k and v columns of ``proj`` in place first."""
     T = proj.shape[0]
+    if dim > 512:
+        raise lib.KernelError("decay_memory: memories of up to 512 rows per head are built")
+    floats = decay_memory_state_floats(heads, dim, vdim)
     if proj.dtype != torch.float32 or proj.stride(1) != 1 or y.shape != (T, heads * vdim) or decay.numel() != heads or \
             max(q_col, k_col) + heads * dim > proj.shape[1] or v_col + heads * vdim > proj.shape[1] or \
-            state.shape[1] < state_off + heads * dim * vdim or activation not in DECAY_ACTIVATIONS:
+            state.shape[1] < state_off + floats or state.stride(1) != 1 or activation not in DECAY_ACTIVATIONS:
         raise lib.KernelError("decay_memory: shapes do not fit")
+    act = DECAY_ACTIVATIONS[activation]
 
-    def walk(mode, max_slices):
-        lib.call("tm_decay_memory", proj.data_ptr(), proj.stride(0), int(q_col), int(k_col), int(v_col),
-                 DECAY_ACTIVATIONS[activation], _req(decay, "decay", torch.float32), _req(state, "state", torch.float32),
+    def walk(mode, max_slices, act):
+        lib.call("tm_decay_memory", proj.data_ptr(), proj.stride(0), int(q_col), int(k_col), int(v_col), act,
+                 _req(decay, "decay", torch.float32), _req(state, "state", torch.float32),
                  state.stride(0), int(state_off), _req(cu_q, "cu_q", torch.int32), _req(state_slots, "state_slots", torch.int32),
                  _req(y, "y", torch.float32), int(n_seqs), heads, dim, vdim, mode, int(slice_len), max_slices,
                  _opt(slice_S, "slice_S", torch.float32), _stream())
 
     if slice_len <= 0:
-        walk(0, 1)
+        walk(0, 1, act)
         return y
     slices = -(-int(max_q_len) // int(slice_len))
-    if slices < 1 or slice_S is None or slice_S.numel() < n_seqs * slices * heads * dim * vdim:
+    if slices < 1 or slice_S is None or slice_S.numel() < n_seqs * slices * floats:
         raise lib.KernelError("decay_memory: scratch for the time slices is missing or too small")
-    walk(1, slices)
+    if act:
+        lib.call("tm_decay_activate", proj.data_ptr(), proj.stride(0), T, int(q_col), int(k_col), int(v_col), heads, dim, vdim,
+                 act, _stream())
+    walk(1, slices, 0)
     lib.call("tm_decay_pass_states", state.data_ptr(), state.stride(0), int(state_off), cu_q.data_ptr(), state_slots.data_ptr(),
              decay.data_ptr(), slice_S.data_ptr(), int(n_seqs), heads, dim, vdim, int(slice_len), slices, _stream())
-    walk(2, slices)
+    walk(2, slices, 0)
     return y

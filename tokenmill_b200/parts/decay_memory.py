@@ -6,7 +6,7 @@ by default. Per head, from S = 0:
 with one constant ``decay_h`` per head and no other scale. The heads side by side are RMS-normed together (one root mean
 square over all heads x dv numbers, a plain weight), multiplied by sigmoid(W_g h), and projected by W_o. The memory, the
 products and the norm are 32-bit in both run dtypes; the projections' product keeps its 32-bit accumulator. Per request
-the mixer keeps S [heads, d, dv] in ONE state slot of 32-bit floats, zero for a new request; prompt portions and single
+the mixer keeps S (a column's rows side by side, [heads, dv, d padded]) in ONE state slot of 32-bit floats, zero for a new request; prompt portions and single
 decoded tokens run the same kernel, which walks a request's tokens in order whatever the cut. A step whose longest
 portion has ``SLICED_FROM`` tokens runs three passes over time slices instead (the slices' own memories side by side,
 then their start memories one after the other, then the slices again with the results): the same sums in another
@@ -58,7 +58,7 @@ class DecayMemoryMixer:
         return None
 
     def state_need(self) -> StateNeed:
-        return StateNeed((self.nh * self.d * self.dv,), "float32")
+        return StateNeed((ops.decay_memory_state_floats(self.nh, self.d, self.dv),), "float32")
 
     def activation_bytes(self, n_tokens: int) -> int:
         elt = 4 if self.dtype == torch.float32 else 2
@@ -75,7 +75,7 @@ class DecayMemoryMixer:
         y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
         sliced = {}
         if step.max_q_len >= SLICED_FROM and step.workspace is not None:
-            need = -(-step.max_q_len // SLICE_LEN) * step.n_seqs * self.nh * self.d * self.dv
+            need = -(-step.max_q_len // SLICE_LEN) * step.n_seqs * ops.decay_memory_state_floats(self.nh, self.d, self.dv)
             if need * 4 <= SLICE_SCRATCH_LIMIT:
                 sliced = dict(max_q_len=step.max_q_len, slice_len=SLICE_LEN,
                               slice_S=step.workspace.get("decay_slice_memories", need, torch.float32))
