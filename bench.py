@@ -818,7 +818,7 @@ def kernel_table(engine, tokens: int, batch: int) -> dict:
         rows = sorted(((e.key, e.device_time_total, e.count) for e in prof.key_averages() if e.device_time_total > 0),
                       key=lambda r: -r[1])
         total = sum(r[1] for r in rows)
-        out[what] = {"total_us": round(total, 1), "kernels": [{"name": k[:90], "us": round(t, 1), "n": n} for k, t, n in rows[:14]]}
+        out[what] = {"total_us": round(total, 1), "kernels": [{"name": k[:90], "us": round(t, 1), "n": n} for k, t, n in rows[:24]]}
         for h in handles:
             cache.free(h)
     return out

@@ -28,6 +28,7 @@ namespace tmk {
 
 constexpr int kScanThreads = 128;
 constexpr int kScanTokens = 16;
+constexpr int kScanFew = 4;            // walks of fewer tokens read W_dt from global memory instead of staging it
 
 // exp(x) to about one unit in the last place (1.05 at worst, a quarter on average): n = round(x / ln 2), r = x - n ln 2 with ln 2 in two pieces (the
 // high one has enough trailing zero bits for n * high to be exact), a degree-7 polynomial on |r| <= 0.347 (remainder below
@@ -115,9 +116,14 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(
   float* S_row = MODE == 0 ? state + (size_t)state_slots[s] * state_stride + state_off + (size_t)(live ? c : 0) * N
                            : slice_S + ((size_t)blockIdx.y * inner + (live ? c : 0)) * N;
 
-  for (int i = threadIdx.x; i < CB * R; i += kScanThreads) {
-    const int cc = i / R, r = i - cc * R;
-    s_w[cc * RS + r] = c0 + cc < inner ? w_dt[(size_t)(c0 + cc) * R + r] : 0.f;
+  // A walk of a few tokens (a decode step) does not stage its rows of W_dt: a channel's lanes share the rank-sized
+  // product, each reading its part of the row from global memory.
+  const bool few = MODE == 0 && q_len < kScanFew;
+  if (!few) {
+    for (int i = threadIdx.x; i < CB * R; i += kScanThreads) {
+      const int cc = i / R, r = i - cc * R;
+      s_w[cc * RS + r] = c0 + cc < inner ? w_dt[(size_t)(c0 + cc) * R + r] : 0.f;
+    }
   }
   for (int i = threadIdx.x; i < CB; i += kScanThreads) {
     s_b[i] = c0 + i < inner ? b_dt[c0 + i] : 0.f;
@@ -151,13 +157,26 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(
       }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < nt * CB; i += kScanThreads) {
-      const int tt = i / CB, cc = i - tt * CB;
-      const float* wr = s_w + cc * RS;
-      const float* low = s_low + tt * R;
-      float acc = 0.f;
-      for (int r = 0; r < R; ++r) acc = fmaf(wr[r], low[r], acc);
-      s_dt[i] = c0 + cc < inner ? softplus32<T>(acc + s_b[cc]) : 0.f;
+    if (few) {
+      const float* wr = w_dt + (size_t)(live ? c : 0) * R;
+      for (int tt = 0; tt < nt; ++tt) {
+        const float* low = s_low + tt * R;
+        float acc = 0.f;
+#pragma unroll 4
+        for (int r = lane; r < R; r += L) acc = fmaf(wr[r], low[r], acc);
+#pragma unroll
+        for (int o = L / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) s_dt[tt * CB + cl] = live ? softplus32<T>(acc + s_b[cl]) : 0.f;
+      }
+    } else {
+      for (int i = threadIdx.x; i < nt * CB; i += kScanThreads) {
+        const int tt = i / CB, cc = i - tt * CB;
+        const float* wr = s_w + cc * RS;
+        const float* low = s_low + tt * R;
+        float acc = 0.f;
+        for (int r = 0; r < R; ++r) acc = fmaf(wr[r], low[r], acc);
+        s_dt[i] = c0 + cc < inner ? softplus32<T>(acc + s_b[cc]) : 0.f;
+      }
     }
     __syncthreads();
 #pragma unroll 4
