@@ -169,13 +169,38 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(
         if (lane == 0) s_dt[tt * CB + cl] = live ? softplus32<T>(acc + s_b[cl]) : 0.f;
       }
     } else {
-      for (int i = threadIdx.x; i < nt * CB; i += kScanThreads) {
-        const int tt = i / CB, cc = i - tt * CB;
-        const float* wr = s_w + cc * RS;
-        const float* low = s_low + tt * R;
-        float acc = 0.f;
-        for (int r = 0; r < R; ++r) acc = fmaf(wr[r], low[r], acc);
-        s_dt[i] = c0 + cc < inner ? softplus32<T>(acc + s_b[cc]) : 0.f;
+      // A thread takes one channel and TPT tokens, so that a number of its row of W_dt serves TPT products; every sum
+      // still runs over the ranks in order. (Rows of tokens past nt hold old numbers; their sums are dropped.)
+      constexpr int TPT = kScanTokens * CB / kScanThreads;
+      const int cc = threadIdx.x % CB, tg = threadIdx.x / CB;
+      const float* wr = s_w + cc * RS;
+      const float* low = s_low + tg * TPT * R;
+      float acc[TPT];
+#pragma unroll
+      for (int j = 0; j < TPT; ++j) acc[j] = 0.f;
+      if ((R & 3) == 0) {
+        for (int r = 0; r < R; r += 4) {
+          const float w0 = wr[r], w1 = wr[r + 1], w2 = wr[r + 2], w3 = wr[r + 3];
+#pragma unroll
+          for (int j = 0; j < TPT; ++j) {
+            const float4 l = *reinterpret_cast<const float4*>(low + j * R + r);
+            acc[j] = fmaf(w0, l.x, acc[j]);
+            acc[j] = fmaf(w1, l.y, acc[j]);
+            acc[j] = fmaf(w2, l.z, acc[j]);
+            acc[j] = fmaf(w3, l.w, acc[j]);
+          }
+        }
+      } else {
+        for (int r = 0; r < R; ++r) {
+          const float wv = wr[r];
+#pragma unroll
+          for (int j = 0; j < TPT; ++j) acc[j] = fmaf(wv, low[j * R + r], acc[j]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < TPT; ++j) {
+        const int tt = tg * TPT + j;
+        if (tt < nt) s_dt[tt * CB + cc] = c0 + cc < inner ? softplus32<T>(acc[j] + s_b[cc]) : 0.f;
       }
     }
     __syncthreads();
