@@ -19,7 +19,8 @@
 // tm_norm_pair_mean: out = (rmsnorm(a) wa + rmsnorm(b) wb) / 2, each row of a and b by its own root mean square.
 //
 // tm_head_norm_gate: y [T, heads, dv] float32 (first divided by den[T, heads], where given) -> each head divided by its
-// root mean square, times weight, times sigmoid(gate pre-activation read from a 32-bit product).
+// root mean square, times weight, times sigmoid or silu of the gate's pre-activation read from a 32-bit product (or
+// no gate).
 #include "common.cuh"
 
 namespace tmk {
@@ -242,12 +243,41 @@ __global__ void __launch_bounds__(256) norm_pair_mean_kernel(const T* __restrict
     out[row + i] = from_float<T>(0.5f * (to_float(a[row + i]) * ra * wa[i] + to_float(b[row + i]) * rb * wb[i]));
 }
 
+// out = sa a + sb b, elementwise in 32-bit, rounded once.
+template <typename T>
+__global__ void __launch_bounds__(256) weighted_pair_kernel(const T* __restrict__ a, const T* __restrict__ b, float sa, float sb,
+                                                            T* __restrict__ out, long long n, int vec) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * (vec ? 4 : 1);
+  if (i0 >= n) return;
+  if (vec) {
+    float x[4], y[4];
+    load4(a + i0, x);
+    load4(b + i0, y);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) x[e] = fmaf(sa, x[e], sb * y[e]);
+    store4(out + i0, x);
+  } else {
+    out[i0] = from_float<T>(fmaf(sa, to_float(a[i0]), sb * to_float(b[i0])));
+  }
+}
+
+// The gate's factor from its pre-activation: sigmoid (act 0) or silu (act 1); no gate: 1.
+__device__ __forceinline__ float gate_value(const float* gate, size_t at, int act) {
+  if (!gate) return 1.0f;
+  const float z = gate[at];
+  const float sg = 1.0f / (1.0f + expf(-z));
+  return act == 1 ? z * sg : sg;
+}
+
 // One warp per (row, head); heads of 512 numbers and more take head_norm_gate_block_kernel.
 template <typename T>
 __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ den,
                                                              const float* __restrict__ gate,
-                                                             long long gate_stride, const float* __restrict__ w, float eps,
-                                                             T* __restrict__ out, int heads, int dv, long long n_pairs) {
+                                                             long long gate_stride, int gate_act, const float* __restrict__ w,
+                                                             float eps, T* __restrict__ out, int heads, int dv,
+                                                             long long n_pairs) {
   pdl_launch_dependents();
   pdl_wait();
   const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -265,8 +295,7 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __rest
   const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
   for (int i = lane; i < dv; i += 32) {
     const int c = hd * dv + i;
-    const float z = gate[(size_t)t * gate_stride + c];
-    out[(size_t)pair * dv + i] = from_float<T>(src[i] / dn * rstd * w[c] / (1.0f + expf(-z)));
+    out[(size_t)pair * dv + i] = from_float<T>(src[i] / dn * rstd * w[c] * gate_value(gate, (size_t)t * gate_stride + c, gate_act));
   }
 }
 
@@ -274,8 +303,8 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __rest
 template <typename T>
 __global__ void __launch_bounds__(256) head_norm_gate_block_kernel(const float* __restrict__ y, const float* __restrict__ den,
                                                                    const float* __restrict__ gate, long long gate_stride,
-                                                                   const float* __restrict__ w, float eps, T* __restrict__ out,
-                                                                   int heads, int dv) {
+                                                                   int gate_act, const float* __restrict__ w, float eps,
+                                                                   T* __restrict__ out, int heads, int dv) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -283,7 +312,7 @@ __global__ void __launch_bounds__(256) head_norm_gate_block_kernel(const float* 
   const long long t = pair / heads;
   const int hd = (int)(pair - t * heads);
   const float* src = y + (size_t)pair * dv;
-  const float* g = gate + (size_t)t * gate_stride + (size_t)hd * dv;
+  const size_t g0 = (size_t)t * gate_stride + (size_t)hd * dv;
   const float dn = den ? den[pair] : 1.f;
   float ss = 0.f;
   for (int i = threadIdx.x; i < dv; i += blockDim.x) {
@@ -292,7 +321,7 @@ __global__ void __launch_bounds__(256) head_norm_gate_block_kernel(const float* 
   }
   const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)dv + eps);
   for (int i = threadIdx.x; i < dv; i += blockDim.x)
-    out[(size_t)pair * dv + i] = from_float<T>(src[i] / dn * rstd * w[hd * dv + i] / (1.0f + expf(-g[i])));
+    out[(size_t)pair * dv + i] = from_float<T>(src[i] / dn * rstd * w[hd * dv + i] * gate_value(gate, g0 + i, gate_act));
 }
 
 }  // namespace tmk
@@ -364,16 +393,28 @@ extern "C" int tm_norm_pair_mean(int dtype, const void* a, const void* b, const 
                                        (const T*)b, wa, wb, eps, (T*)out, H, (int)(H % 4 == 0)))
 }
 
+// a, b, out: n numbers each; out = sa a + sb b.
+extern "C" int tm_weighted_pair(int dtype, const void* a, const void* b, float sa, float sb, void* out, long long n,
+                                cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int vec = n % 4 == 0 && !(((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15);
+  const long long threads = vec ? n / 4 : n;
+  TM_BY_DTYPE(dtype, return launch_pdl(weighted_pair_kernel<T>, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, stream,
+                                       (const T*)a, (const T*)b, sa, sb, (T*)out, n, vec))
+}
+
 // y [T, heads * dv] float; den [T, heads] float or null; gate: float pre-activations, element (t, c) at
-// gate + t * gate_stride + c; w [heads * dv].
-extern "C" int tm_head_norm_gate(int dtype, const float* y, const float* den, const float* gate, long long gate_stride, const float* w,
-                                 float eps, void* out, int T_rows, int heads, int dv, cudaStream_t stream) {
+// gate + t * gate_stride + c, through a sigmoid (gate_act 0) or silu (1), or null for no gate; w [heads * dv].
+extern "C" int tm_head_norm_gate(int dtype, const float* y, const float* den, const float* gate, long long gate_stride,
+                                 int gate_act, const float* w, float eps, void* out, int T_rows, int heads, int dv,
+                                 cudaStream_t stream) {
   if (T_rows <= 0) return 0;
+  if (gate_act != 0 && gate_act != 1) return TM_ERR_UNSUPPORTED_SHAPE;
   const long long pairs = (long long)T_rows * heads;
   if (dv >= 512) {
     TM_BY_DTYPE(dtype, return launch_pdl(head_norm_gate_block_kernel<T>, dim3((unsigned)pairs), dim3(256), 0, stream, y, den, gate,
-                                         gate_stride, w, eps, (T*)out, heads, dv))
+                                         gate_stride, gate_act, w, eps, (T*)out, heads, dv))
   }
   TM_BY_DTYPE(dtype, return launch_pdl(head_norm_gate_kernel<T>, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, stream, y,
-                                       den, gate, gate_stride, w, eps, (T*)out, heads, dv, pairs))
+                                       den, gate, gate_stride, gate_act, w, eps, (T*)out, heads, dv, pairs))
 }

@@ -34,7 +34,8 @@ __global__ void __launch_bounds__(256) relu2_kernel(const T* __restrict__ in, T*
 // One warp per token over its E logits (32-bit, from a matrix product; `bias` is added here when given).
 __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                                        int* __restrict__ top_idx, float* __restrict__ top_w,
-                                                       float* __restrict__ dense_w, int T_, int E, int top) {
+                                                       float* __restrict__ dense_w, int T_, int E, int top, long long ld,
+                                                       int scoring) {
   extern __shared__ float sm[];               // per warp: E logits
   pdl_launch_dependents();
   pdl_wait();
@@ -43,7 +44,7 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
   if (t >= T_) return;
   float* logit = sm + warp * E;
   for (int e = lane; e < E; e += 32) {
-    logit[e] = logits[(size_t)t * E + e] + (bias ? bias[e] : 0.f);
+    logit[e] = logits[(size_t)t * ld + e] + (bias ? bias[e] : 0.f);
     dense_w[(size_t)t * E + e] = 0.f;
   }
   __syncwarp();
@@ -63,7 +64,8 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
     if (k == 0) best0 = bv;
-    const float ex = expf(bv - best0);
+    // scoring 0: a softmax over the chosen logits; 1: each chosen logit's sigmoid as it is
+    const float ex = scoring == 1 ? 1.0f / (1.0f + expf(-bv)) : expf(bv - best0);
     denom += ex;
     if (lane == 0) {
       top_idx[(size_t)t * top + k] = bi;
@@ -74,7 +76,7 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
   }
   if (lane == 0) {
     for (int k = 0; k < top; ++k) {
-      const float wv = top_w[(size_t)t * top + k] / denom;
+      const float wv = scoring == 1 ? top_w[(size_t)t * top + k] : top_w[(size_t)t * top + k] / denom;
       top_w[(size_t)t * top + k] = wv;
       dense_w[(size_t)t * E + top_idx[(size_t)t * top + k]] = wv;
     }
@@ -214,6 +216,42 @@ __global__ void __launch_bounds__(256) add_scaled_rows_kernel(T* __restrict__ ou
     out[(size_t)t * H + i] = from_float<T>(fmaf(wv, to_float(x[(size_t)t * H + i]), to_float(out[(size_t)t * H + i])));
 }
 
+// Experts whose weight multiplies their INPUT: expert(w h) = W_down (silu(w g) * (w u)) with g = W_gate h, u = W_up h,
+// so the two products run on h itself and the weight enters here (exact zeros for experts not chosen). Block
+// (token, expert); expert number E is a shared expert of Fs numbers that every token uses, its output times
+// sigmoid(shared_logit[t]). A token's row of gu is [E x (gate F | up F) | shared gate Fs | shared up Fs], of act
+// [E x F | Fs].
+template <typename T>
+__global__ void __launch_bounds__(128) glu_routed_in_kernel(const T* __restrict__ gu, const float* __restrict__ dense_w,
+                                                            T* __restrict__ act, int E, int F, int Fs,
+                                                            const float* __restrict__ shared_logit, long long shared_ld) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, e = blockIdx.y;
+  const size_t in_row = (size_t)E * 2 * F + 2 * (size_t)Fs, out_row = (size_t)E * F + Fs;
+  if (e == E) {
+    const float sg = shared_logit ? 1.0f / (1.0f + expf(-shared_logit[(size_t)t * shared_ld])) : 1.0f;
+    const T* g = gu + (size_t)t * in_row + (size_t)E * 2 * F;
+    T* o = act + (size_t)t * out_row + (size_t)E * F;
+    for (int i = threadIdx.x; i < Fs; i += blockDim.x) {
+      const float gv = to_float(g[i]);
+      o[i] = from_float<T>(gv / (1.0f + expf(-gv)) * to_float(g[Fs + i]) * sg);
+    }
+    return;
+  }
+  const float wv = dense_w[(size_t)t * E + e];
+  const T* g = gu + (size_t)t * in_row + (size_t)e * 2 * F;
+  T* o = act + (size_t)t * out_row + (size_t)e * F;
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    float v = 0.f;
+    if (wv != 0.f) {
+      const float gv = wv * to_float(g[i]);
+      v = gv / (1.0f + expf(-gv)) * (wv * to_float(g[F + i]));
+    }
+    o[i] = from_float<T>(v);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) glu_routed_kernel(const T* __restrict__ gu, const float* __restrict__ dense_w,
                                                          T* __restrict__ act, int E, int F) {
@@ -293,12 +331,29 @@ extern "C" int tm_relu2(int dtype, const void* in, void* out, long long total, c
 
 // logits [T, E] float (bias [E] float added when given); top_idx [T, top] int; top_w [T, top], dense_w [T, E] float.
 extern "C" int tm_moe_topk(const float* logits, const float* bias, int* top_idx, float* top_w, float* dense_w, int T,
-                           int E, int top, cudaStream_t stream) {
+                           int E, int top, long long ld, int scoring, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (top < 1 || top > E || E > 2048) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (top < 1 || top > E || E > 2048 || ld < E || (scoring != 0 && scoring != 1)) return TM_ERR_UNSUPPORTED_SHAPE;
   const int warps = 4;
   return tmk::launch_pdl(tmk::moe_topk_kernel, dim3((T + warps - 1) / warps), dim3(warps * 32),
-                         (size_t)warps * E * sizeof(float), stream, logits, bias, top_idx, top_w, dense_w, T, E, top);
+                         (size_t)warps * E * sizeof(float), stream, logits, bias, top_idx, top_w, dense_w, T, E, top, ld,
+                         scoring);
+}
+
+// gu [T, E * 2 F + 2 Fs], act [T, E F + Fs] dtype; dense_w [T, E] float; shared_logit: float, token t's at
+// shared_logit[t * shared_ld] (null with Fs > 0: the shared expert is not gated).
+extern "C" int tm_glu_routed_in(int dtype, const void* gu, const float* dense_w, void* act, int T, int E, int F, int Fs,
+                                const float* shared_logit, long long shared_ld, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E > 65534 || E < 1 || F < 1 || Fs < 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  const dim3 grid(T, E + (Fs > 0 ? 1 : 0));
+  if (dtype == TM_DTYPE_F32)
+    return tmk::launch_pdl(tmk::glu_routed_in_kernel<float>, grid, dim3(128), 0, stream, (const float*)gu, dense_w,
+                           (float*)act, E, F, Fs, shared_logit, shared_ld);
+  if (dtype == TM_DTYPE_BF16)
+    return tmk::launch_pdl(tmk::glu_routed_in_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)gu,
+                           dense_w, (__nv_bfloat16*)act, E, F, Fs, shared_logit, shared_ld);
+  return TM_ERR_BAD_DTYPE;
 }
 
 // gu [T, E, 2, F], act [T, E, F] dtype; dense_w [T, E] float.

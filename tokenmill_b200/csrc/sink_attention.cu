@@ -7,8 +7,8 @@
 // tm_qk_norm_rope_write, one block per token, reads the token's row of a 32-bit projection
 //   [q (H d) | k (G d) | v (G dv) | g (gate_cols)]        (g only with gate_out; k and v only with has_kv: a layer that
 //                                                          reads another layer's keys and values has none)
-// and writes: q, RMS-normed over all its H d numbers at once (weight wq; skipped when wq is null) and rotated, in the
-// activation dtype; [k | v] to the token's cache row, k normed over its G d numbers (wk) and rotated; sigmoid(g) in
+// and writes: q, RMS-normed over all its H d numbers at once (weight wq; skipped when wq is null; with head_norm every
+// head of q and k by its own root mean square instead, the weights then optional) and rotated, in the activation dtype; [k | v] to the token's cache row, k normed over its G d numbers (wk) and rotated; sigmoid(g) in
 // 32-bit. With temp_every > 0 the query is multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) at position
 // p (32-bit). The rotation pairs dimension i with i + rot_dims / 2 inside each head; angles come from 32-bit tables
 // [positions, rot_dims / 2].
@@ -30,8 +30,9 @@ __global__ void __launch_bounds__(256) qk_norm_rope_write_kernel(
     const float* __restrict__ wk, float eps, const int* __restrict__ positions, const float* __restrict__ cos_t,
     const float* __restrict__ sin_t, int n_positions, const int* __restrict__ slot_map, T* __restrict__ q_out,
     T* __restrict__ cache, float* __restrict__ gate_out, int gate_cols, int has_kv, float temp_coef, int temp_every,
-    int* __restrict__ error) {
-  extern __shared__ __align__(16) float staged[];    // the token's q and k columns: read once, used three times
+    int head_norm, int* __restrict__ error) {
+  extern __shared__ __align__(16) float staged[];    // the token's q and k columns: read once, used three times; then,
+                                                     // with a norm per head, one factor per head (H + G floats)
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -56,9 +57,23 @@ __global__ void __launch_bounds__(256) qk_norm_rope_write_kernel(
     else sk += v * v;
   }
   float rq = 1.f, rk = 1.f;
-  if (wq) rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + eps);
-  if (wk) rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + eps);
-  if (!wq && !wk) __syncthreads();
+  float* head_r = staged + nq + nk;
+  if (head_norm) {          // every head of q and of k by its own root mean square (weights optional)
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    for (int u = warp; u < H + (has_kv ? G : 0); u += n_warps) {
+      const float* hp = staged + (size_t)u * d;
+      float ss = 0.f;
+      for (int i = lane; i < d; i += 32) ss = fmaf(hp[i], hp[i], ss);
+      ss = warp_sum(ss);
+      if (lane == 0) head_r[u] = 1.0f / sqrtf(ss / (float)d + eps);
+    }
+    __syncthreads();
+  } else {
+    if (wq) rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + eps);
+    if (wk) rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + eps);
+    if (!wq && !wk) __syncthreads();
+  }
   const int slot = slot_map ? slot_map[t] : -1;
   T* crow = slot >= 0 ? cache + (size_t)slot * (nk + nv) : nullptr;
   for (int idx = threadIdx.x; idx < nq + nk; idx += blockDim.x) {
@@ -67,7 +82,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_write_kernel(
     const int i = is_q ? idx : idx - nq;
     const float* src = is_q ? staged : staged + nq;
     const float* w = is_q ? wq : wk;
-    const float r = is_q ? rq : rk;
+    const float r = head_norm ? head_r[idx / d] : (is_q ? rq : rk);
     const int e = i % d;
     float v = src[i] * r * (w ? w[i] : 1.f);
     if (e < half) {
@@ -97,7 +112,8 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attention_kernel(
     const T* __restrict__ q, const T* __restrict__ cache, int row_width, int v_off, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_before, const int* __restrict__ tile_seq,
     const int* __restrict__ tile_row0, const float* __restrict__ gate, T* __restrict__ out, int H, int G, int d, int dv,
-    int page_size, float scale, float softcap, int window, int keep_first, int sink, int gate_wide) {
+    int page_size, float scale, float softcap, int window, int keep_first, int sink, int gate_wide,
+    float* __restrict__ cross_out) {
   extern __shared__ __align__(16) float smem[];
   const int KS = d + 1;                           // padded key row: lanes read different rows, same column
   float* qs = smem;                               // [32][d]
@@ -108,7 +124,9 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attention_kernel(
   pdl_wait();
   const int s = tile_seq[blockIdx.x];
   const int row0 = tile_row0[blockIdx.x];
-  const int kvh = blockIdx.y;
+  // cross_out: blockIdx.y = key head * G + value head, and the head's weights meet the values of that value head
+  const int kvh = cross_out ? blockIdx.y / G : blockIdx.y;
+  const int vh = cross_out ? blockIdx.y - kvh * G : kvh;
   const int Gq = H / G;
   const int q_start = cu_q[s];
   const int q_len = cu_q[s + 1] - q_start;
@@ -160,7 +178,7 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attention_kernel(
       const T* src = cache;
       if (seen) src += ((size_t)table[j / page_size] * page_size + (j % page_size)) * row_width;
       const T* kp = src + kvh * d;
-      const T* vp = src + v_off + kvh * dv;
+      const T* vp = src + v_off + vh * dv;
       for (int e = part; e < d; e += 8) ks[jj * KS + e] = seen ? to_float(kp[e]) : 0.f;
       for (int e = part; e < dv; e += 8) vs[jj * dv + e] = seen ? to_float(vp[e]) : 0.f;
     }
@@ -219,6 +237,15 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attention_kernel(
     if (row >= n_rows) continue;
     const int tok = q_start + row / Gq, head = kvh * Gq + row % Gq;
     float f = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+    if (cross_out) {
+      float* o32 = cross_out + (((size_t)tok * H + head) * G + vh) * dv;
+#pragma unroll
+      for (int dd = 0; dd < NDV; ++dd) {
+        const int e = lane + 32 * dd;
+        if (e < dv) o32[e] = acc[i][dd] * f;
+      }
+      continue;
+    }
     if (gate && !gate_wide) f *= gate[(size_t)tok * H + head];
     T* o = out + ((size_t)tok * H + head) * dv;
     const float* gw = (gate && gate_wide) ? gate + ((size_t)tok * H + head) * dv : nullptr;
@@ -234,7 +261,8 @@ template <typename T>
 int launch_sink_attention(const void* q, const void* cache, int row_width, int v_off, const int* block_table, int bt_stride,
                           const int* cu_q, const int* kv_before, const int* tile_seq, const int* tile_row0, int n_tiles,
                           const float* gate, void* out, int H, int G, int d, int dv, int page_size, float scale,
-                          float softcap, int window, int keep_first, int sink, int gate_wide, cudaStream_t stream) {
+                          float softcap, int window, int keep_first, int sink, int gate_wide, float* cross_out,
+                          cudaStream_t stream) {
   const size_t smem = ((size_t)kSinkTileRows * d + (size_t)kSinkKeyTile * (d + 1) + (size_t)kSinkKeyTile * dv) * sizeof(float);
   if (smem > 220 * 1024 || dv > 256 || H % G) return TM_ERR_UNSUPPORTED_SHAPE;
   const int nd = (dv + 31) / 32;
@@ -245,9 +273,9 @@ int launch_sink_attention(const void* q, const void* cache, int row_width, int v
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
       if (e != cudaSuccess) return (int)e;                                                                        \
     }                                                                                                             \
-    return launch_pdl(kern, dim3(n_tiles, G), dim3(kSinkWarps * 32), smem, stream, (const T*)q, (const T*)cache,  \
-                      row_width, v_off, block_table, bt_stride, cu_q, kv_before, tile_seq, tile_row0, gate, (T*)out, H, G, \
-                      d, dv, page_size, scale, softcap, window, keep_first, sink, gate_wide);                     \
+    return launch_pdl(kern, dim3(n_tiles, cross_out ? G * G : G), dim3(kSinkWarps * 32), smem, stream, (const T*)q, \
+                      (const T*)cache, row_width, v_off, block_table, bt_stride, cu_q, kv_before, tile_seq, tile_row0, gate, \
+                      (T*)out, H, G, d, dv, page_size, scale, softcap, window, keep_first, sink, gate_wide, cross_out); \
   }
   switch (nd) {
     TM_SINK_CASE(1) TM_SINK_CASE(2) TM_SINK_CASE(3) TM_SINK_CASE(4) TM_SINK_CASE(5) TM_SINK_CASE(6) TM_SINK_CASE(7)
@@ -265,12 +293,12 @@ int launch_sink_attention(const void* q, const void* cache, int row_width, int v
 extern "C" int tm_qk_norm_rope_write(int dtype, const float* proj, long long ld, int H, int G, int d, int dv, int rot_dims,
                                      const float* wq, const float* wk, float eps, const int* positions, const float* cos_t,
                                      const float* sin_t, int n_positions, const int* slot_map, void* q_out, void* cache,
-                                     float* gate_out, int gate_cols, int has_kv, float temp_coef, int temp_every, int T_rows,
-                                     int* error, cudaStream_t stream) {
+                                     float* gate_out, int gate_cols, int has_kv, float temp_coef, int temp_every, int head_norm,
+                                     int T_rows, int* error, cudaStream_t stream) {
   if (T_rows <= 0) return 0;
   if (rot_dims % 2 || rot_dims > d || rot_dims < 0 || H <= 0 || G <= 0 || temp_every < 0) return TM_ERR_UNSUPPORTED_SHAPE;
   if (!has_kv && (cache || wk)) return TM_ERR_UNSUPPORTED_SHAPE;
-  const size_t smem = (size_t)(H + G) * d * sizeof(float);
+  const size_t smem = ((size_t)(H + G) * d + (head_norm ? H + G : 0)) * sizeof(float);
   if (smem > 200 * 1024) return TM_ERR_UNSUPPORTED_SHAPE;
   if (smem > 40 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(tmk::qk_norm_rope_write_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -281,30 +309,32 @@ extern "C" int tm_qk_norm_rope_write(int dtype, const float* proj, long long ld,
   if (dtype == TM_DTYPE_F32)
     return tmk::launch_pdl(tmk::qk_norm_rope_write_kernel<float>, dim3(T_rows), dim3(256), smem, stream, proj, ld, H, G, d, dv,
                            rot_dims, wq, wk, eps, positions, cos_t, sin_t, n_positions, slot_map, (float*)q_out,
-                           (float*)cache, gate_out, gate_cols, has_kv, temp_coef, temp_every, error);
+                           (float*)cache, gate_out, gate_cols, has_kv, temp_coef, temp_every, head_norm, error);
   if (dtype == TM_DTYPE_BF16)
     return tmk::launch_pdl(tmk::qk_norm_rope_write_kernel<__nv_bfloat16>, dim3(T_rows), dim3(256), smem, stream, proj, ld, H, G,
                            d, dv, rot_dims, wq, wk, eps, positions, cos_t, sin_t, n_positions, slot_map,
                            (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, gate_out, gate_cols, has_kv, temp_coef, temp_every,
-                           error);
+                           head_norm, error);
   return TM_ERR_BAD_DTYPE;
 }
 
 // q [T, H, d]; cache [pages, page_size, row_width] with head g's key at g * d and its value at v_off + g * dv; tiles of 32
-// (token, head in group) rows; gate [T, H] float (gate_wide: [T, H, dv]) or null; out [T, H, dv].
+// (token, head in group) rows; gate [T, H] float (gate_wide: [T, H, dv]) or null; out [T, H, dv]. cross_out [T, H, G, dv]
+// float (then out and gate are not used): every head's softmax weights applied to the values of each of the G value heads.
 extern "C" int tm_sink_attention(int dtype, const void* q, const void* cache, int row_width, int v_off,
                                  const int* block_table, int bt_stride, const int* cu_q, const int* kv_before,
                                  const int* tile_seq, const int* tile_row0, int n_tiles, const float* gate, void* out, int H,
                                  int G, int d, int dv, int page_size, float scale, float softcap, int window, int keep_first,
-                                 int sink, int gate_wide, cudaStream_t stream) {
+                                 int sink, int gate_wide, float* cross_out, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (cross_out && gate) return TM_ERR_UNSUPPORTED_SHAPE;
   if (dtype == TM_DTYPE_F32)
     return tmk::launch_sink_attention<float>(q, cache, row_width, v_off, block_table, bt_stride, cu_q, kv_before, tile_seq,
                                              tile_row0, n_tiles, gate, out, H, G, d, dv, page_size, scale, softcap, window,
-                                             keep_first, sink, gate_wide, stream);
+                                             keep_first, sink, gate_wide, cross_out, stream);
   if (dtype == TM_DTYPE_BF16)
     return tmk::launch_sink_attention<__nv_bfloat16>(q, cache, row_width, v_off, block_table, bt_stride, cu_q, kv_before,
                                                      tile_seq, tile_row0, n_tiles, gate, out, H, G, d, dv, page_size, scale,
-                                                     softcap, window, keep_first, sink, gate_wide, stream);
+                                                     softcap, window, keep_first, sink, gate_wide, cross_out, stream);
   return TM_ERR_BAD_DTYPE;
 }

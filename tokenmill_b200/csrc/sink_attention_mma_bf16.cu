@@ -34,7 +34,8 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_before,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0, const float* __restrict__ gate,
     __nv_bfloat16* __restrict__ out, int H, int G, int page_size, float scale, float softcap, int window, int keep_first,
-    int sink, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int gate_wide) {
+    int sink, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int gate_wide,
+    float* __restrict__ cross_out) {
   constexpr int THREADS = kSmWarps * 32;
   constexpr int CHK = DK / 8, CHV = DV / 8;     // 16-byte chunks per key / value row
   constexpr int TPR = THREADS / kSmBN;          // threads that share one key row when loading (2)
@@ -48,7 +49,10 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
 
   pdl_launch_dependents();
   pdl_wait();
-  const int s = tile_seq[blockIdx.x], row0 = tile_row0[blockIdx.x], kvh = blockIdx.y;
+  // cross_out: blockIdx.y = key head * G + value head, and the head's weights meet the values of that value head
+  const int s = tile_seq[blockIdx.x], row0 = tile_row0[blockIdx.x];
+  const int kvh = cross_out ? blockIdx.y / G : blockIdx.y;
+  const int vh = cross_out ? blockIdx.y - kvh * G : kvh;
   const int Gq = H / G;
   const int q_start = cu_q[s], q_len = cu_q[s + 1] - q_start, before = kv_before[s];
   const int n_rows = min(kSmBM, q_len * Gq - row0);
@@ -118,7 +122,7 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
       src = ((size_t)page * page_size + (j % page_size)) * row_width;
     }
     const __nv_bfloat16* kp = cache + src + kvh * DK;
-    const __nv_bfloat16* vp = cache + src + v_off + kvh * DV;
+    const __nv_bfloat16* vp = cache + src + v_off + vh * DV;
 #pragma unroll
     for (int i = 0; i < CHK / TPR; ++i) {
       const int c = part * (CHK / TPR) + i;
@@ -256,7 +260,7 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
     for (int hh = 0; hh < 2; ++hh) {
       if (p_row[hh] < 0) continue;
       const int r = warp * 16 + (lane >> 2) + hh * 8;
-      const size_t prow = (((size_t)blockIdx.x * G + kvh) * n_splits + split) * kSmBM + r;
+      const size_t prow = (((size_t)blockIdx.x * gridDim.y + blockIdx.y) * n_splits + split) * kSmBM + r;
       float* dst = part_o + prow * DV;
 #pragma unroll
       for (int t = 0; t < NT; ++t)
@@ -269,6 +273,13 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
   for (int hh = 0; hh < 2; ++hh) {
     if (p_row[hh] < 0) continue;
     float f = l_run[hh] > 0.f ? 1.0f / l_run[hh] : 0.f;
+    if (cross_out) {
+      float* dst32 = cross_out + (o_row[hh] * G + vh) * DV;
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+        *reinterpret_cast<float2*>(dst32 + t * 8 + cpair) = make_float2(o[t][2 * hh] * f, o[t][2 * hh + 1] * f);
+      continue;
+    }
     if (gate && !gate_wide) f *= gate[o_row[hh]];
     __nv_bfloat16* dst = out + o_row[hh] * DV;
     const float* gw = (gate && gate_wide) ? gate + o_row[hh] * DV : nullptr;
@@ -286,15 +297,17 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
 __global__ void __launch_bounds__(256) sink_attention_combine_kernel(
     const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ cu_q,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0, const float* __restrict__ gate,
-    __nv_bfloat16* __restrict__ out, int H, int G, int dv, int n_splits, int gate_wide) {
+    __nv_bfloat16* __restrict__ out, int H, int G, int dv, int n_splits, int gate_wide, float* __restrict__ cross_out) {
   pdl_launch_dependents();
   pdl_wait();
-  const int s = tile_seq[blockIdx.x], row0 = tile_row0[blockIdx.x], kvh = blockIdx.y;
+  const int s = tile_seq[blockIdx.x], row0 = tile_row0[blockIdx.x];
+  const int kvh = cross_out ? blockIdx.y / G : blockIdx.y;
+  const int vh = cross_out ? blockIdx.y - kvh * G : kvh;
   const int Gq = H / G;
   const int q_start = cu_q[s], q_len = cu_q[s + 1] - q_start;
   const int n_rows = min(kSmBM, q_len * Gq - row0);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const size_t base = ((size_t)blockIdx.x * G + kvh) * n_splits;
+  const size_t base = ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * n_splits;
   for (int r = warp; r < n_rows; r += 8) {
     float M = -INFINITY;
     for (int z = 0; z < n_splits; ++z) M = fmaxf(M, part_ml[((base + z) * kSmBM + r) * 2]);
@@ -314,7 +327,8 @@ __global__ void __launch_bounds__(256) sink_attention_combine_kernel(
         const float mz = part_ml[((base + z) * kSmBM + r) * 2];
         if (mz != -INFINITY) acc += part_o[((base + z) * kSmBM + r) * dv + e] * exp2f(mz - M);
       }
-      out[o_row * dv + e] = __float2bfloat16_rn(acc * f * (gw ? gw[e] : 1.0f));
+      if (cross_out) cross_out[(o_row * G + vh) * dv + e] = acc * f;
+      else out[o_row * dv + e] = __float2bfloat16_rn(acc * f * (gw ? gw[e] : 1.0f));
     }
   }
 }
@@ -324,7 +338,7 @@ int launch_sink_attention_mma(const void* q, const void* cache, int row_width, i
                               int bt_stride, const int* cu_q, const int* kv_before, const int* tile_seq,
                               const int* tile_row0, int n_tiles, const float* gate, void* out, int H, int G, int page_size,
                               float scale, float softcap, int window, int keep_first, int sink, int n_splits, float* part_o,
-                              float* part_ml, int gate_wide, cudaStream_t stream) {
+                              float* part_ml, int gate_wide, float* cross_out, cudaStream_t stream) {
   constexpr int STAGES = (DK + DV) >= 256 ? 2 : 3;
   const int smem = STAGES * kSmBN * (DK + DV) * 2;
   auto kern = sink_attention_mma_kernel<DK, DV, STAGES>;
@@ -332,13 +346,15 @@ int launch_sink_attention_mma(const void* q, const void* cache, int row_width, i
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
   }
-  const int st = launch_pdl(kern, dim3(n_tiles, G, n_splits), dim3(kSmWarps * 32), (size_t)smem, stream,
+  const int gy = cross_out ? G * G : G;
+  const int st = launch_pdl(kern, dim3(n_tiles, gy, n_splits), dim3(kSmWarps * 32), (size_t)smem, stream,
                             (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, row_width, v_off, block_table, bt_stride, cu_q,
                             kv_before, tile_seq, tile_row0, gate, (__nv_bfloat16*)out, H, G, page_size, scale, softcap, window,
-                            keep_first, sink, n_splits, part_o, part_ml, gate_wide);
+                            keep_first, sink, n_splits, part_o, part_ml, gate_wide, cross_out);
   if (st != 0 || n_splits == 1) return st;
-  return launch_pdl(sink_attention_combine_kernel, dim3(n_tiles, G), dim3(256), 0, stream, (const float*)part_o,
-                    (const float*)part_ml, cu_q, tile_seq, tile_row0, gate, (__nv_bfloat16*)out, H, G, DV, n_splits, gate_wide);
+  return launch_pdl(sink_attention_combine_kernel, dim3(n_tiles, gy), dim3(256), 0, stream, (const float*)part_o,
+                    (const float*)part_ml, cu_q, tile_seq, tile_row0, gate, (__nv_bfloat16*)out, H, G, DV, n_splits, gate_wide,
+                    cross_out);
 }
 
 }  // namespace tmk
@@ -347,21 +363,24 @@ int launch_sink_attention_mma(const void* q, const void* cache, int row_width, i
 // v_off + g * dv (row_width and v_off multiples of 8); tiles of 64 (token, head in group) rows of one request; gate
 // [T, H] float (gate_wide: [T, H, dv]) or null; out [T, H, dv] bfloat16. d and dv each 32, 64 or 128; the scale positive. n_splits > 1: a
 // tile's key blocks are dealt out over that many blocks, through part_o [n_tiles * G * n_splits, 64, dv] and part_ml
-// [n_tiles * G * n_splits, 64, 2] float, and merged by a second launch.
+// [n_tiles * G * n_splits, 64, 2] float, and merged by a second launch. cross_out [T, H, G, dv] float (then out and gate
+// are not used, and the partial results have G times the rows): every head's softmax weights applied to the values of
+// each of the G value heads.
 extern "C" int tm_sink_attention_mma_bf16(const void* q, const void* cache, int row_width, int v_off,
                                           const int* block_table, int bt_stride, const int* cu_q, const int* kv_before,
                                           const int* tile_seq, const int* tile_row0, int n_tiles, const float* gate,
                                           void* out, int H, int G, int d, int dv, int page_size, float scale, float softcap,
                                           int window, int keep_first, int sink, int n_splits, float* part_o, float* part_ml,
-                                          int gate_wide, cudaStream_t stream) {
+                                          int gate_wide, float* cross_out, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (cross_out && gate) return TM_ERR_UNSUPPORTED_SHAPE;
   if (n_splits < 1 || (n_splits > 1 && (!part_o || !part_ml))) return TM_ERR_SCRATCH_TOO_SMALL;
   if (G <= 0 || H % G || page_size <= 0 || (row_width & 7) || (v_off & 7) || !(scale > 0.f)) return TM_ERR_UNSUPPORTED_SHAPE;
 #define TM_SM_CASE(DKK, DVV)                                                                                          \
   if (d == DKK && dv == DVV)                                                                                          \
     return tmk::launch_sink_attention_mma<DKK, DVV>(q, cache, row_width, v_off, block_table, bt_stride, cu_q, kv_before, \
                                                     tile_seq, tile_row0, n_tiles, gate, out, H, G, page_size, scale, softcap, \
-                                                    window, keep_first, sink, n_splits, part_o, part_ml, gate_wide, stream);
+                                                    window, keep_first, sink, n_splits, part_o, part_ml, gate_wide, cross_out, stream);
   TM_SM_CASE(32, 32) TM_SM_CASE(32, 64) TM_SM_CASE(32, 128) TM_SM_CASE(64, 32) TM_SM_CASE(64, 64) TM_SM_CASE(64, 128)
   TM_SM_CASE(128, 32) TM_SM_CASE(128, 64) TM_SM_CASE(128, 128)
 #undef TM_SM_CASE

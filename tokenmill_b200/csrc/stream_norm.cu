@@ -2,7 +2,7 @@
 //
 // tm_stream_norm, one block per row. The residual of a token is S streams of H numbers, [T, S, H] in 32-bit. In one pass
 // over the row the kernel
-//   * starts the streams, every one as table[id] + pos_table[position] (summed in 32-bit), when ids are given;
+//   * starts the streams, every one as table[id] * table_scale + pos_table[position] (32-bit), when ids are given;
 //   * or takes in the previous sublayer's result y = branch + row_scale * branch2 (each optional):
 //     x_t <- sum_s mix[s, t] x_s + out[t] y, all streams from the old ones (mix null: x_t <- x_t + y);
 //   * reads the streams as u = sum_s in[s] x_s (in null: the plain sum);
@@ -11,7 +11,7 @@
 // With `rows` only those rows are read and normed, and the residual is left as it is (the model's last norm). S = 1
 // with no mix is the ordinary residual stream. Everything is 32-bit; the output is rounded once.
 //
-// tm_softcap: x <- cap * tanh(x / cap) in place (32-bit logits).
+// tm_softcap: x <- cap * tanh(scale x / cap) in place (32-bit logits); cap 0: x <- scale x.
 #include "common.cuh"
 
 namespace tmk {
@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(
     const T* __restrict__ branch2, const float* __restrict__ row_scale, long long row_scale_stride,
     const float* __restrict__ mix, const float* __restrict__ out_w, const float* __restrict__ in_w,
     const int* __restrict__ rows, int mode, const float* __restrict__ alpha_p, const float* __restrict__ w,
-    const float* __restrict__ b, float eps, T* __restrict__ out) {
+    const float* __restrict__ b, float eps, T* __restrict__ out, float table_scale) {
   constexpr int NS = SC ? SC : kMaxStreams;
   __shared__ float red[32];
   __shared__ float coef[kMaxStreams * kMaxStreams + 2 * kMaxStreams];
@@ -69,6 +69,8 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(
     if (start) {
       float v[W];
       ldw<W>(e_row + i, v);
+#pragma unroll
+      for (int e = 0; e < W; ++e) v[e] *= table_scale;
       if (p_row) {
         float pv[W];
         ldw<W>(p_row + i, pv);
@@ -151,7 +153,7 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(
       // (the last norm of a model: read-only; recompute as above)
       float xs[kMaxStreams];
       if (start) {
-        float v = to_float(e_row[i]);
+        float v = to_float(e_row[i]) * table_scale;
         if (p_row) v += to_float(p_row[i]);
         for (int s = 0; s < S; ++s) xs[s] = v;
       } else {
@@ -175,18 +177,21 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(
   }
 }
 
-__global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ x, long long n, float cap) {
+__global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ x, long long n, float cap, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) x[i] = cap * tanhf(x[i] / cap);
+  if (i >= n) return;
+  const float z = x[i] * scale;
+  x[i] = cap > 0.f ? cap * tanhf(z / cap) : z;
 }
 
 template <typename T>
 int launch_stream_norm(float* resid, int S, int H, const int* ids, const void* table, const int* positions, const void* pos_table,
                        const void* branch, const void* branch2, const float* row_scale, long long row_scale_stride,
                        const float* mix, const float* out_w, const float* in_w, const int* rows, int mode, const float* alpha,
-                       const float* w, const float* b, float eps, void* out, int n_rows, cudaStream_t stream) {
+                       const float* w, const float* b, float eps, void* out, int n_rows, float table_scale,
+                       cudaStream_t stream) {
   // four elements per access where every row starts on 16 bytes
   const uintptr_t all = (uintptr_t)resid | (uintptr_t)table | (uintptr_t)pos_table | (uintptr_t)branch | (uintptr_t)branch2 |
                         (uintptr_t)w | (uintptr_t)b | (uintptr_t)out;
@@ -194,7 +199,7 @@ int launch_stream_norm(float* resid, int S, int H, const int* ids, const void* t
 #define TM_STREAMS(SC_, W_)                                                                                                  \
   return launch_pdl(stream_norm_kernel<T, SC_, W_>, dim3(n_rows), dim3(256), 0, stream, resid, S, H, ids, (const T*)table,   \
                     positions, (const T*)pos_table, (const T*)branch, (const T*)branch2, row_scale, row_scale_stride, mix,   \
-                    out_w, in_w, rows, mode, alpha, w, b, eps, (T*)out)
+                    out_w, in_w, rows, mode, alpha, w, b, eps, (T*)out, table_scale)
   if (wide) {
     if (S == 1) TM_STREAMS(1, 4);
     if (S == 2) TM_STREAMS(2, 4);
@@ -215,22 +220,22 @@ extern "C" int tm_stream_norm(int dtype, float* resid, int S, int H, const int* 
                               const void* pos_table, const void* branch, const void* branch2, const float* row_scale,
                               long long row_scale_stride, const float* mix, const float* out_w, const float* in_w, const int* rows,
                               int mode, const float* alpha, const float* w, const float* b, float eps, void* out, int n_rows,
-                              cudaStream_t stream) {
+                              float table_scale, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (S < 1 || S > tmk::kMaxStreams || H < 1 || (mode != 0 && mode != 1) || (mode == 0 && !alpha)) return TM_ERR_UNSUPPORTED_SHAPE;
   if (ids && (branch || branch2)) return TM_ERR_UNSUPPORTED_SHAPE;
   if (dtype == TM_DTYPE_F32)
     return tmk::launch_stream_norm<float>(resid, S, H, ids, table, positions, pos_table, branch, branch2, row_scale,
-                                          row_scale_stride, mix, out_w, in_w, rows, mode, alpha, w, b, eps, out, n_rows, stream);
+                                          row_scale_stride, mix, out_w, in_w, rows, mode, alpha, w, b, eps, out, n_rows, table_scale, stream);
   if (dtype == TM_DTYPE_BF16)
     return tmk::launch_stream_norm<__nv_bfloat16>(resid, S, H, ids, table, positions, pos_table, branch, branch2, row_scale,
                                                   row_scale_stride, mix, out_w, in_w, rows, mode, alpha, w, b, eps, out, n_rows,
-                                                  stream);
+                                                  table_scale, stream);
   return TM_ERR_BAD_DTYPE;
 }
 
-extern "C" int tm_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+extern "C" int tm_softcap(float* x, long long n, float cap, float scale, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (!(cap > 0.f)) return TM_ERR_UNSUPPORTED_SHAPE;
-  return tmk::launch_pdl(tmk::softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, cap);
+  if (!(cap >= 0.f)) return TM_ERR_UNSUPPORTED_SHAPE;
+  return tmk::launch_pdl(tmk::softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, cap, scale);
 }

@@ -1,12 +1,14 @@
 """Compile the sm_100a kernels with nvcc into shared libraries, at first use.
 
 The sources under ``tokenmill_b200/csrc`` have no dependency beyond the CUDA toolkit (no torch or
-pybind headers), so a cold build takes well under a minute. They form four libraries, each built when a
+pybind headers), so a cold build takes well under a minute. They form five libraries, each built when a
 kernel of it is first called, so that a model compiles what it runs and no more: ``main`` (everything the
 Qwen2 path, the sampler and the shape-generic kernels need), ``hybrid`` (the kernels of latent attention,
 state-space layers, routed experts, 32-bit pair norms), ``gated`` (gated convolutional blocks, windowed attention
-with a sink, matrix memory) and ``streams`` (several residual streams behind a norm, the selective scan, linear
-attention with a decay, and the files of the other two whose kernels such a model also runs). A file may be part
+with a sink, matrix memory), ``streams`` (several residual streams behind a norm, the selective scan, linear
+attention with a decay, and the files of the other two whose kernels such a model also runs) and ``delta`` (matrix
+memories with a decay per token and the delta rule, short convolutions with carried inputs, and the files of the others
+that a model of such layers beside windowed attention and routed experts runs). A file may be part
 of several libraries; the 32-bit matrix product is in all.
 A library is written next to the
 sources (``csrc/_build``) when that folder can be written, else under the system's temporary folder;
@@ -50,11 +52,13 @@ HYBRID = ("norm_pair.cu", "latent_attention.cu", "latent_attention_mma_bf16.cu",
 GATED = ("gated_block.cu", "sink_attention.cu", "sink_attention_mma_bf16.cu", "matrix_memory.cu")
 STREAMS = ("stream_norm.cu", "selective_scan.cu", "decay_memory.cu", "routed_ffn.cu", "ssm_scan.cu", "sink_attention.cu",
            "sink_attention_mma_bf16.cu", "gated_block.cu")
+DELTA = ("gated_memory.cu", "stream_norm.cu", "sink_attention.cu", "sink_attention_mma_bf16.cu", "gated_block.cu",
+         "routed_ffn.cu")
 SHARED = ("gemm_f32.cu",)
-GROUPS = ("main", "hybrid", "gated", "streams")
+GROUPS = ("main", "hybrid", "gated", "streams", "delta")
 _PREFIX = {"main": "libtokenmill_kernels_", "hybrid": "libtokenmill_hybrid_", "gated": "libtokenmill_gated_",
-           "streams": "libtokenmill_streams_"}
-_FILES = {"hybrid": HYBRID, "gated": GATED, "streams": STREAMS}
+           "streams": "libtokenmill_streams_", "delta": "libtokenmill_delta_"}
+_FILES = {"hybrid": HYBRID, "gated": GATED, "streams": STREAMS, "delta": DELTA}
 
 
 def sources(group: str = "main") -> list[Path]:

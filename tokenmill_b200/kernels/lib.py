@@ -79,24 +79,33 @@ _SIGNATURES: dict[str, list] = {
     "tm_ssm_scan": [_I, _P, _I, _P, _LL, _I, _P, _P, _P, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
     "tm_ssm_pass_states": [_P, _LL, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "tm_relu2": [_I, _P, _P, _LL, _P],
-    "tm_moe_topk": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "tm_moe_topk": [_P, _P, _P, _P, _P, _I, _I, _I, _LL, _I, _P],
+    "tm_glu_routed_in": [_I, _P, _P, _P, _I, _I, _I, _I, _P, _LL, _P],
     "tm_glu_routed": [_I, _P, _P, _P, _I, _I, _I, _P],
     "tm_gemm_f32_nt_batched": [_P, _LL, _I, _P, _LL, _P, _LL, _I, _I, _I, _I, _I, _P],
     "tm_gated_add_rmsnorm": [_I, _P, _P, _P, _LL, _P, _P, _P, _F, _P, _P, _F, _P, _I, _I, _P],
     "tm_canon_conv": [_I, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _P],
     "tm_glu": [_I, _I, _P, _P, _I, _I, _P],
     "tm_norm_pair_mean": [_I, _P, _P, _P, _P, _F, _P, _I, _I, _P],
-    "tm_head_norm_gate": [_I, _P, _P, _P, _LL, _P, _F, _P, _I, _I, _I, _P],
+    "tm_weighted_pair": [_I, _P, _P, _F, _F, _P, _LL, _P],
+    "tm_head_norm_gate": [_I, _P, _P, _P, _LL, _I, _P, _F, _P, _I, _I, _I, _P],
     "tm_qk_norm_rope_write": [_I, _P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _F, _I, _I,
-                              _P, _P],
-    "tm_sink_attention": [_I, _P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _P],
+                              _I, _P, _P],
+    "tm_sink_attention": [_I, _P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _P,
+                          _P],
     "tm_sink_attention_mma_bf16": [_P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I,
-                                   _P, _P, _I, _P],
+                                   _P, _P, _I, _P, _P],
     "tm_moe_choose": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "tm_act_routed": [_I, _P, _P, _I, _P, _I, _I, _I, _P],
     "tm_add_scaled_rows": [_I, _P, _P, _P, _I, _I, _P],
-    "tm_stream_norm": [_I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _P, _P, _P, _F, _P, _I, _P],
-    "tm_softcap": [_P, _LL, _F, _P],
+    "tm_stream_norm": [_I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _P, _P, _P, _F, _P, _I, _F, _P],
+    "tm_softcap": [_P, _LL, _F, _F, _P],
+    "tm_gated_memory": [_P, _LL, _I, _I, _I, _P, _I, _I, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "tm_gated_memory_pass_states": [_P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "tm_short_conv_state": [_P, _LL, _I, _I, _I, _P, _P, _P, _LL, _LL, _P, _P, _P, _I, _P, _LL, _I, _I, _P],
+    "tm_delta_prepare": [_P, _LL, _I, _I, _I, _I, _F, _F, _P, _LL, _I, _I, _P, _P, _I, _P, _I, _P],
+    "tm_forget_gate_prepare": [_P, _LL, _I, _I, _I, _P, _P, _I, _P],
+    "tm_talk_mix": [_I, _P, _P, _P, _I, _I, _I, _I, _P],
     "tm_selective_scan": [_I, _P, _I, _P, _LL, _I, _P, _LL, _I, _I, _P, _P, _P, _P, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I,
                           _P, _P, _P],
     "tm_selective_pass_states": [_I, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
@@ -119,14 +128,17 @@ _BY_FILE = {
     "latent_attention_mma_bf16.cu": {"tm_latent_attention_mma_bf16"},
     "ssm_scan.cu": {"tm_conv_silu_state", "tm_ssm_scan", "tm_ssm_pass_states"},
     "routed_ffn.cu": {"tm_relu2", "tm_moe_topk", "tm_glu_routed", "tm_gemm_f32_nt_batched", "tm_moe_choose", "tm_act_routed",
-                      "tm_add_scaled_rows"},
-    "gated_block.cu": {"tm_gated_add_rmsnorm", "tm_canon_conv", "tm_glu", "tm_norm_pair_mean", "tm_head_norm_gate"},
+                      "tm_add_scaled_rows", "tm_glu_routed_in"},
+    "gated_block.cu": {"tm_gated_add_rmsnorm", "tm_canon_conv", "tm_glu", "tm_norm_pair_mean", "tm_head_norm_gate",
+                       "tm_weighted_pair"},
     "sink_attention.cu": {"tm_qk_norm_rope_write", "tm_sink_attention"},
     "sink_attention_mma_bf16.cu": {"tm_sink_attention_mma_bf16"},
     "matrix_memory.cu": {"tm_matrix_memory", "tm_matrix_memory_pass_states"},
     "stream_norm.cu": {"tm_stream_norm", "tm_softcap"},
     "selective_scan.cu": {"tm_selective_scan", "tm_selective_pass_states"},
     "decay_memory.cu": {"tm_decay_memory", "tm_decay_pass_states", "tm_decay_activate"},
+    "gated_memory.cu": {"tm_gated_memory", "tm_gated_memory_pass_states", "tm_short_conv_state", "tm_delta_prepare",
+                        "tm_forget_gate_prepare", "tm_talk_mix"},
 }
 _BOTH = {"tm_gemm_f32_nt"}            # in every library
 _GROUPS_OF: dict[str, list[str]] = {}     # entry point -> the libraries that hold it, in the order of kernels/build.py

@@ -1017,8 +1017,42 @@ def moe_route(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top: 
     tw = torch.empty((T, top), dtype=torch.float32, device=x.device)
     dense = torch.empty((T, E), dtype=torch.float32, device=x.device)
     lib.call("tm_moe_topk", _req(logits, "logits", torch.float32), _opt(bias, "bias", torch.float32), idx.data_ptr(),
-             tw.data_ptr(), dense.data_ptr(), T, E, int(top), _stream())
+             tw.data_ptr(), dense.data_ptr(), T, E, int(top), E, 0, _stream())
     return idx, tw, dense
+
+
+MOE_SCORING = {"softmax_of_chosen": 0, "sigmoid": 1}
+
+
+def moe_topk(logits: torch.Tensor, experts: int, top: int, scoring: str):
+    """logits [T, >= experts] float32 (further columns are not read) -> (top_idx [T, top] int32, top_w [T, top], dense_w
+    [T, experts] float32): the ``top`` largest logits, the lowest index winning a tie; weights a softmax over the chosen
+    logits (``softmax_of_chosen``) or each chosen logit's sigmoid as it is (``sigmoid``)."""
+    T = logits.shape[0]
+    if scoring not in MOE_SCORING or logits.dim() != 2 or logits.shape[1] < experts or logits.stride(1) != 1:
+        raise lib.KernelError("moe_topk: shapes do not fit")
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    tw = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    dense = torch.empty((T, experts), dtype=torch.float32, device=logits.device)
+    lib.call("tm_moe_topk", _req(logits, "logits", torch.float32), None, idx.data_ptr(), tw.data_ptr(), dense.data_ptr(), T,
+             int(experts), int(top), logits.stride(0), MOE_SCORING[scoring], _stream())
+    return idx, tw, dense
+
+
+def glu_routed_in(gu: torch.Tensor, dense_w: torch.Tensor, act: torch.Tensor, E: int, F: int, shared: int = 0,
+                  shared_logit: torch.Tensor | None = None) -> torch.Tensor:
+    """Experts whose weight multiplies their input. gu [T, E * 2 F + 2 shared] (per expert gate rows then up rows, then the
+    shared expert's) -> act [T, E F + shared] = silu(w gate) * (w up) for the chosen experts, zero for the others, and
+    silu(gate) * up * sigmoid(shared_logit) for the shared expert; shared_logit [T] float32 (may be strided) or None."""
+    T = gu.shape[0]
+    if gu.shape[1] != E * 2 * F + 2 * shared or act.shape != (T, E * F + shared) or dense_w.shape != (T, E) or \
+            (shared_logit is not None and (shared_logit.dim() != 1 or shared_logit.numel() != T or
+                                           shared_logit.dtype != torch.float32)):
+        raise lib.KernelError("glu_routed_in: shapes do not fit")
+    lib.call("tm_glu_routed_in", _code(gu.dtype), _req(gu, "gu"), _req(dense_w, "dense_w", torch.float32),
+             _req(act, "act", gu.dtype), T, E, F, int(shared), shared_logit.data_ptr() if shared_logit is not None else None,
+             shared_logit.stride(0) if shared_logit is not None else 0, _stream())
+    return act
 
 
 def glu_routed(gu: torch.Tensor, dense_w: torch.Tensor, act: torch.Tensor, E: int, F: int) -> torch.Tensor:
@@ -1148,16 +1182,30 @@ def norm_pair_mean(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch
     return out
 
 
-def head_norm_gate(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, heads: int,
-                   out: torch.Tensor, den: torch.Tensor | None = None) -> torch.Tensor:
+def weighted_pair(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float, out: torch.Tensor) -> torch.Tensor:
+    """out = sa * a + sb * b, elementwise (32-bit arithmetic, one rounding)."""
+    if b.shape != a.shape or out.shape != a.shape or b.dtype != a.dtype:
+        raise lib.KernelError("weighted_pair: shapes do not fit")
+    lib.call("tm_weighted_pair", _code(a.dtype), _req(a, "a"), _req(b, "b"), float(sa), float(sb), _req(out, "out", a.dtype),
+             a.numel(), _stream())
+    return out
+
+
+HEAD_GATES = {"sigmoid": 0, "silu": 1}
+
+
+def head_norm_gate(y: torch.Tensor, gate: torch.Tensor | None, weight: torch.Tensor, eps: float, heads: int,
+                   out: torch.Tensor, den: torch.Tensor | None = None, gate_act: str = "sigmoid") -> torch.Tensor:
     """y [T, heads * dv] float32 (divided by den [T, heads] first, where given): each head by its own root mean square,
-    times weight, times sigmoid(gate); gate [T, heads * dv] float32 pre-activations (rows may be strided)."""
+    times weight [heads * dv], times sigmoid(gate) or silu(gate) (``gate_act``); gate [T, heads * dv] float32
+    pre-activations (rows may be strided), or None for no gate."""
     T, inner = y.shape
-    if inner % heads or gate.shape != y.shape or gate.stride(1) != 1 or gate.dtype != torch.float32 or \
-            weight.numel() != inner or out.shape != y.shape or (den is not None and den.shape != (T, heads)):
+    if inner % heads or weight.numel() != inner or out.shape != y.shape or (den is not None and den.shape != (T, heads)) or \
+            gate_act not in HEAD_GATES or \
+            (gate is not None and (gate.shape != y.shape or gate.stride(1) != 1 or gate.dtype != torch.float32)):
         raise lib.KernelError("head_norm_gate: shapes do not fit")
     lib.call("tm_head_norm_gate", _code(out.dtype), _req(y, "y", torch.float32), _opt(den, "den", torch.float32),
-             gate.data_ptr(), gate.stride(0),
+             gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0, HEAD_GATES[gate_act],
              _req(weight, "weight", torch.float32), float(eps), _req(out, "out"), T, heads, inner // heads, _stream())
     return out
 
@@ -1166,11 +1214,12 @@ def qk_norm_rope_write(proj: torch.Tensor, *, heads: int, kv_heads: int, dim: in
                        wq: torch.Tensor | None, wk: torch.Tensor | None, eps: float, positions: torch.Tensor,
                        cos: torch.Tensor, sin: torch.Tensor, slot_map: torch.Tensor | None, q_out: torch.Tensor,
                        cache: torch.Tensor | None, gate_out: torch.Tensor | None, has_kv: bool = True,
-                       q_temp: tuple[float, int] | None = None) -> None:
+                       q_temp: tuple[float, int] | None = None, head_norm: bool = False) -> None:
     """proj [T, >= H d + G d + G dv (+ gate columns)] float32 (rows may be strided) -> q_out [T, H d] normed and rotated,
     the token's cache row [k | v], gate_out [T, H] or [T, H dv] = sigmoid of the last columns. ``has_kv`` False: the row
     is [q | g] only (a layer that reads another layer's keys and values). ``q_temp`` (coef, every): the query is
-    multiplied by 1 + coef ln(floor((p + 1) / every) + 1) at position p."""
+    multiplied by 1 + coef ln(floor((p + 1) / every) + 1) at position p. ``head_norm``: every head of q and of k is divided
+    by its own root mean square (wq and wk then optional) instead of the whole projections by theirs."""
     T = proj.shape[0]
     gate_cols = gate_out.shape[1] if gate_out is not None else 0
     need = heads * dim + (kv_heads * (dim + vdim) if has_kv else 0) + gate_cols
@@ -1187,7 +1236,7 @@ def qk_norm_rope_write(proj: torch.Tensor, *, heads: int, kv_heads: int, dim: in
              _req(positions, "positions", torch.int32), _req(cos, "cos", torch.float32), _req(sin, "sin", torch.float32),
              cos.shape[0], _opt(slot_map, "slot_map", torch.int32) if cache is not None else None, _req(q_out, "q_out"),
              _opt(cache, "cache", dt), _opt(gate_out, "gate_out", torch.float32), gate_cols, int(bool(has_kv)), coef, every,
-             T, _tc_flag(proj.device).data_ptr(), _stream())
+             int(bool(head_norm)), T, _tc_flag(proj.device).data_ptr(), _stream())
 
 
 SINK_TILE_ROWS = 32
@@ -1204,21 +1253,29 @@ def sink_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tens
                    kv_before: torch.Tensor, tile_seq: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int,
                    gate: torch.Tensor | None, out: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int,
                    scale: float, softcap: float, window: int, keep_first: int, sink: bool,
-                   tensor_cores: bool = False, n_splits: int = 1, part: torch.Tensor | None = None) -> torch.Tensor:
+                   tensor_cores: bool = False, n_splits: int = 1, part: torch.Tensor | None = None,
+                   cross_out: torch.Tensor | None = None) -> torch.Tensor:
     """q [T, H d]; cache [pages, page_size, 1, G d + G dv]; tiles of 32 (``tensor_cores``: 64) (token, head in group)
     rows of one request; gate [T, H] (or [T, H dv]: one per output number) float32 or None; out [T, H dv]. ``n_splits`` > 1 (tensor cores only): a tile's
     key blocks dealt out over that many blocks and merged, through ``part``, float32 scratch of
-    n_tiles * G * n_splits * 64 * (dv + 2) numbers."""
+    n_tiles * G * n_splits * 64 * (dv + 2) numbers. ``cross_out`` [T, H * G * dv] float32 (then ``out`` may be None and
+    there is no gate; the scratch has G times the numbers): every head's softmax weights applied to the values of each of
+    the G value heads, [T, H, G, dv], for a mixer that mixes the heads' weights afterwards."""
     T = q.shape[0]
     row = kv_heads * (dim + vdim)
-    if cache.shape[-1] != row or q.shape != (T, heads * dim) or out.shape != (T, heads * vdim) or \
+    if cache.shape[-1] != row or q.shape != (T, heads * dim) or \
+            (cross_out is None and out.shape != (T, heads * vdim)) or \
+            (cross_out is not None and (cross_out.shape != (T, heads * kv_heads * vdim) or cross_out.dtype != torch.float32
+                                        or gate is not None)) or \
             (gate is not None and tuple(gate.shape) not in ((T, heads), (T, heads * vdim))):
         raise lib.KernelError("sink_attention: shapes do not fit")
     wide = int(gate is not None and gate.shape[1] != heads)
+    cross = _opt(cross_out, "cross_out", torch.float32)
+    out_ptr = _req(out, "out", q.dtype) if out is not None else None
     if tensor_cores:
         part_o = part_ml = None
         if n_splits > 1:
-            rows64 = int(n_tiles) * kv_heads * int(n_splits) * SINK_TC_TILE_ROWS
+            rows64 = int(n_tiles) * kv_heads * (kv_heads if cross_out is not None else 1) * int(n_splits) * SINK_TC_TILE_ROWS
             if part is None or part.dtype != torch.float32 or part.numel() < rows64 * (vdim + 2):
                 raise lib.KernelError("sink_attention: scratch for the key splits is missing or too small")
             part_o, part_ml = part.data_ptr(), part.data_ptr() + rows64 * vdim * 4
@@ -1226,17 +1283,17 @@ def sink_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tens
                  kv_heads * dim, _req(block_table, "block_table", torch.int32), block_table.stride(0),
                  _req(cu_q, "cu_q", torch.int32), _req(kv_before, "kv_before", torch.int32),
                  _req(tile_seq, "tile_seq", torch.int32), _req(tile_row0, "tile_row0", torch.int32), int(n_tiles),
-                 _opt(gate, "gate", torch.float32), _req(out, "out", torch.bfloat16), heads, kv_heads, dim, vdim,
+                 _opt(gate, "gate", torch.float32), out_ptr, heads, kv_heads, dim, vdim,
                  cache.shape[1], float(scale), float(softcap), int(window), int(keep_first), int(bool(sink)),
-                 int(n_splits), part_o, part_ml, wide, _stream())
-        return out
+                 int(n_splits), part_o, part_ml, wide, cross, _stream())
+        return out if cross_out is None else cross_out
     lib.call("tm_sink_attention", _code(q.dtype), _req(q, "q"), _req(cache, "cache", q.dtype), row, kv_heads * dim,
              _req(block_table, "block_table", torch.int32), block_table.stride(0), _req(cu_q, "cu_q", torch.int32),
              _req(kv_before, "kv_before", torch.int32), _req(tile_seq, "tile_seq", torch.int32),
              _req(tile_row0, "tile_row0", torch.int32), int(n_tiles), _opt(gate, "gate", torch.float32),
-             _req(out, "out", q.dtype), heads, kv_heads, dim, vdim, cache.shape[1], float(scale), float(softcap),
-             int(window), int(keep_first), int(bool(sink)), wide, _stream())
-    return out
+             out_ptr, heads, kv_heads, dim, vdim, cache.shape[1], float(scale), float(softcap),
+             int(window), int(keep_first), int(bool(sink)), wide, cross, _stream())
+    return out if cross_out is None else cross_out
 
 
 MEMORY_THREADS = 256
@@ -1312,8 +1369,8 @@ def stream_norm(resid: torch.Tensor, streams: int, out: torch.Tensor, *, kind: s
                 ids: torch.Tensor | None = None, table: torch.Tensor | None = None, positions: torch.Tensor | None = None,
                 pos_table: torch.Tensor | None = None, branch: torch.Tensor | None = None, branch2: torch.Tensor | None = None,
                 row_scale: torch.Tensor | None = None, mix: torch.Tensor | None = None, out_w: torch.Tensor | None = None,
-                in_w: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> torch.Tensor:
-    """resid [T, streams * H] float32: the streams of every token side by side. Starts them all as table[ids] (+
+                in_w: torch.Tensor | None = None, rows: torch.Tensor | None = None, table_scale: float = 1.0) -> torch.Tensor:
+    """resid [T, streams * H] float32: the streams of every token side by side. Starts them all as table[ids] * table_scale (+
     pos_table[positions]), or takes in y = branch + row_scale * branch2: x_t <- sum_s mix[s, t] x_s + out_w[t] y (no mix:
     x_t <- x_t + y); reads u = sum_s in_w[s] x_s (no in_w: the sum) and writes out = norm(u): ``dyt`` tanh(alpha u) w + b, or
     ``rms``. With ``rows`` only those rows are normed and the residual stays as it is."""
@@ -1333,13 +1390,14 @@ def stream_norm(resid: torch.Tensor, streams: int, out: torch.Tensor, *, kind: s
              row_scale.data_ptr() if row_scale is not None else None, row_scale.stride(0) if row_scale is not None else 0,
              _opt(mix, "mix", torch.float32), _opt(out_w, "out_w", torch.float32), _opt(in_w, "in_w", torch.float32),
              _opt(rows, "rows", torch.int32), STREAM_NORMS[kind], _opt(alpha, "alpha", torch.float32),
-             _req(weight, "weight", torch.float32), _opt(bias, "bias", torch.float32), float(eps), _req(out, "out"), n_rows, _stream())
+             _req(weight, "weight", torch.float32), _opt(bias, "bias", torch.float32), float(eps), _req(out, "out"), n_rows,
+             float(table_scale), _stream())
     return out
 
 
-def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
-    """x <- cap * tanh(x / cap), in place (float32)."""
-    lib.call("tm_softcap", _req(x, "x", torch.float32), x.numel(), float(cap), _stream())
+def softcap_(x: torch.Tensor, cap: float, scale: float = 1.0) -> torch.Tensor:
+    """x <- cap * tanh(scale x / cap), in place (float32); cap 0: x <- scale x."""
+    lib.call("tm_softcap", _req(x, "x", torch.float32), x.numel(), float(cap), float(scale), _stream())
     return x
 
 
@@ -1435,3 +1493,124 @@ def decay_memory(proj: torch.Tensor, *, q_col: int, k_col: int, v_col: int, acti
              decay.data_ptr(), slice_S.data_ptr(), int(n_seqs), heads, dim, vdim, int(slice_len), slices, _stream())
     walk(2, slices, 0)
     return y
+
+
+# --- matrix memories with a decay per token, the delta rule, short convolutions with carried inputs ---------------
+
+
+def gated_memory_state_floats(heads: int, dim: int, vdim: int) -> int:
+    """Floats of a request's memories as the kernel lays them out: [heads][vdim][d_pad], a column's rows side by side, 16
+    rows on each of the power-of-two lanes that share a column (csrc/gated_memory.cu)."""
+    parts = 1
+    while parts * 16 < dim:
+        parts *= 2
+    return heads * vdim * parts * 16
+
+
+def gated_memory_slice_floats(heads: int, dim: int, vdim: int, delta: bool) -> int:
+    """Floats of one time slice's record in scratch: its own memory and what it does to the memory it starts from (one
+    more column, or ``dim`` more with the delta rule)."""
+    return gated_memory_state_floats(heads, dim, vdim + (dim if delta else 1))
+
+
+def gated_memory(proj: torch.Tensor, *, q_col: int, k_col: int, v_col: int, gb: torch.Tensor | None, rule: str,
+                 state: torch.Tensor, state_off: int, cu_q: torch.Tensor, state_slots: torch.Tensor, y: torch.Tensor,
+                 n_seqs: int, heads: int, qk_heads: int, dim: int, vdim: int, max_q_len: int = 0, slice_len: int = 0,
+                 slice_S: torch.Tensor | None = None) -> torch.Tensor:
+    """proj [T, P] float32 (rows may be strided) with q and k (qk_heads x dim) and v (heads x vdim) at the given columns;
+    head h reads q/k head h // (heads // qk_heads). ``rule``: "delta": S <- g S, u = beta (v - S^T k), S <- S + k u^T with
+    (g, beta) = gb [T, 2 heads] float32; "forget": the columns at k_col hold f, S <- diag(f) S + (1 - f) v^T, gb unused;
+    "decay": S <- g S + k v^T. y [T, heads * vdim] float32 = S^T q after the write. A request's memories
+    (``gated_memory_state_floats`` floats) live ``state_off`` floats into its slot. ``slice_len`` > 0: three passes over
+    time slices of that many tokens (for long prompt portions) through ``slice_S`` (n_seqs * slices records of
+    ``gated_memory_slice_floats`` floats), slices = ceil(max_q_len / slice_len)."""
+    T = proj.shape[0]
+    if rule not in ("delta", "forget", "decay") or dim > 512:
+        raise lib.KernelError("gated_memory: rules delta, forget and decay over memories of up to 512 rows are built")
+    row_decay, delta = int(rule == "forget"), int(rule == "delta")
+    floats = gated_memory_state_floats(heads, dim, vdim)
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or y.shape != (T, heads * vdim) or heads % qk_heads or \
+            max(q_col, k_col) + qk_heads * dim > proj.shape[1] or v_col + heads * vdim > proj.shape[1] or \
+            state.shape[1] < state_off + floats or state.stride(1) != 1 or \
+            (not row_decay and (gb is None or gb.shape != (T, 2 * heads))):
+        raise lib.KernelError("gated_memory: shapes do not fit")
+
+    def walk(mode, max_slices):
+        lib.call("tm_gated_memory", proj.data_ptr(), proj.stride(0), int(q_col), int(k_col), int(v_col),
+                 _opt(gb, "gb", torch.float32) if not row_decay else None, row_decay, delta,
+                 _req(state, "state", torch.float32), state.stride(0), int(state_off), _req(cu_q, "cu_q", torch.int32),
+                 _req(state_slots, "state_slots", torch.int32), _req(y, "y", torch.float32), int(n_seqs), heads, qk_heads, dim,
+                 vdim, mode, int(slice_len), max_slices, _opt(slice_S, "slice_S", torch.float32), _stream())
+
+    if slice_len <= 0:
+        walk(0, 1)
+        return y
+    slices = -(-int(max_q_len) // int(slice_len))
+    if slices < 1 or slice_S is None or slice_S.numel() < n_seqs * slices * gated_memory_slice_floats(heads, dim, vdim, bool(delta)):
+        raise lib.KernelError("gated_memory: scratch for the time slices is missing or too small")
+    walk(1, slices)
+    lib.call("tm_gated_memory_pass_states", state.data_ptr(), state.stride(0), int(state_off), cu_q.data_ptr(),
+             state_slots.data_ptr(), slice_S.data_ptr(), delta, int(n_seqs), heads, dim, vdim, int(slice_len), slices, _stream())
+    walk(2, slices)
+    return y
+
+
+def short_conv_state(proj: torch.Tensor, col0: int, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
+                     state_off: int, cu_q: torch.Tensor, seq_of_token: torch.Tensor, state_slots: torch.Tensor,
+                     out: torch.Tensor, out_col0: int = 0, activation: str | None = None) -> torch.Tensor:
+    """A causal convolution over time on ``channels`` columns of proj [T, P] float32 from column col0 (rows may be
+    strided): out[t, out_col0 + c] = act(sum_j weight[c, j] u[t - taps + 1 + j, c]) with u = proj + bias and act silu or
+    none; weight [channels, taps] float32. A request's last taps - 1 inputs (bias included) are carried ``state_off`` floats
+    into its slot, [taps - 1, channels]; zeros for a new request. out float32 [T, >= out_col0 + channels]."""
+    T = proj.shape[0]
+    channels, taps = weight.shape
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or col0 + channels > proj.shape[1] or out.dtype != torch.float32 or \
+            out.stride(1) != 1 or out.shape[0] != T or out_col0 + channels > out.shape[1] or \
+            (bias is not None and bias.numel() != channels) or activation not in (None, "silu") or \
+            state.shape[1] < state_off + (taps - 1) * channels or state.stride(1) != 1:
+        raise lib.KernelError("short_conv_state: shapes do not fit")
+    lib.call("tm_short_conv_state", proj.data_ptr(), proj.stride(0), int(col0), channels, taps,
+             _req(weight, "weight", torch.float32), _opt(bias, "bias", torch.float32), _req(state, "state", torch.float32),
+             state.stride(0), int(state_off), _req(cu_q, "cu_q", torch.int32), _req(seq_of_token, "seq_of_token", torch.int32),
+             _req(state_slots, "state_slots", torch.int32), int(activation == "silu"), out.data_ptr(), out.stride(0),
+             int(out_col0), T, _stream())
+    return out
+
+
+def delta_prepare(x: torch.Tensor, q_col: int, k_col: int, qk_heads: int, dim: int, q_scale: float, unit_eps: float,
+                  raw: torch.Tensor, b_col: int, a_col: int, A_log: torch.Tensor, dt_bias: torch.Tensor, heads: int,
+                  gb: torch.Tensor) -> torch.Tensor:
+    """In place on x [T, P] float32: every q and k head (qk_heads x dim at the given columns) becomes x / sqrt(sum x^2 +
+    unit_eps), q also times q_scale. From raw [T, R] float32 (rows may be strided): gb [T, 2 heads] <- (exp(-exp(A_log)
+    softplus(raw[a_col + h] + dt_bias)), sigmoid(raw[b_col + h]))."""
+    T = x.shape[0]
+    if x.dtype != torch.float32 or x.stride(1) != 1 or max(q_col, k_col) + qk_heads * dim > x.shape[1] or \
+            raw.dtype != torch.float32 or raw.stride(1) != 1 or max(a_col, b_col) + heads > raw.shape[1] or \
+            gb.shape != (T, 2 * heads) or A_log.numel() != heads or dt_bias.numel() != heads:
+        raise lib.KernelError("delta_prepare: shapes do not fit")
+    lib.call("tm_delta_prepare", x.data_ptr(), x.stride(0), int(q_col), int(k_col), int(qk_heads), int(dim), float(q_scale),
+             float(unit_eps), raw.data_ptr(), raw.stride(0), int(b_col), int(a_col), _req(A_log, "A_log", torch.float32),
+             _req(dt_bias, "dt_bias", torch.float32), int(heads), _req(gb, "gb", torch.float32), T, _stream())
+    return gb
+
+
+def forget_gate_prepare(x: torch.Tensor, q_col: int, f_col: int, n: int, low: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+    """In place on x [T, P] float32 (rows may be strided): the n columns at q_col <- silu, the n columns at f_col <-
+    low + (1 - low) sigmoid(. + bias); low, bias [n] float32."""
+    if x.dtype != torch.float32 or x.stride(1) != 1 or max(q_col, f_col) + n > x.shape[1] or low.numel() != n or \
+            (bias is not None and bias.numel() != n):
+        raise lib.KernelError("forget_gate_prepare: shapes do not fit")
+    lib.call("tm_forget_gate_prepare", x.data_ptr(), x.stride(0), int(q_col), int(f_col), int(n), _req(low, "low", torch.float32),
+             _opt(bias, "bias", torch.float32), x.shape[0], _stream())
+    return x
+
+
+def talk_mix(cross: torch.Tensor, talk: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, vdim: int) -> torch.Tensor:
+    """cross [T, heads * kv_heads * vdim] float32 (head g's softmax weights applied to the values of every value head);
+    talk [heads, heads] float32; out [T, heads * vdim] <- sum_g talk[h, g] cross[t, g, value head of h]."""
+    T = cross.shape[0]
+    if cross.shape != (T, heads * kv_heads * vdim) or talk.shape != (heads, heads) or out.shape != (T, heads * vdim):
+        raise lib.KernelError("talk_mix: shapes do not fit")
+    lib.call("tm_talk_mix", _code(out.dtype), _req(cross, "cross", torch.float32), _req(talk, "talk", torch.float32),
+             _req(out, "out"), T, heads, kv_heads, vdim, _stream())
+    return out

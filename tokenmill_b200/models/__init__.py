@@ -1,3 +1,3 @@
 """Architectures. Importing this package registers them."""
 
-from . import bobunex, dibizen, kutirax, qwen2  # noqa: F401
+from . import bobunex, dibizen, gofezen, kutirax, qwen2  # noqa: F401

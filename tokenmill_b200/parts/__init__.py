@@ -1,6 +1,6 @@
 """Parts a layer is made of. Importing this package registers the built-in kinds."""
 
-from . import (attention, block, decay_memory, latent_attention, matrix_memory, norm, pair_mixer, rope, routed, sink_attention,  # noqa: F401
+from . import (attention, block, decay_memory, gated_memory, latent_attention, matrix_memory, norm, pair_mixer, rope, routed, sink_attention,  # noqa: F401
                state_space, swiglu)
 from .base import LayerCache, StepInputs
 from .model import CacheGroup, CacheLayout, DecoderModel

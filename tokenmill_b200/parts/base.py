@@ -38,7 +38,8 @@ class LayerCache:
 
     k, v: [pages, page_size, kv_heads, head_dim] views of the entry's group pool (None for a mixer
     without paged needs). group: index of the block-table / slot-map set in StepInputs. writes:
-    False when the entry reads another entry's cache. state: [slots, *shape] per-request state of the mixer;
+    False when the entry reads another entry's cache. state: [slots, *shape] per-request state of the mixer
+    (from ``state_off`` floats into the slot on, for mixers that honour it);
     block_state: the same for the block arrangement, where it keeps some. A cache of one plane has no v."""
 
     k: torch.Tensor | None = None
@@ -47,6 +48,8 @@ class LayerCache:
     writes: bool = True
     state: torch.Tensor | None = None
     block_state: torch.Tensor | None = None
+    state_off: int = 0      # floats into a request's slot of ``state`` at which the mixer's own state starts (a mixer
+                            # made of mixers hands each of them its share of one slot this way)
 
 
 class PrefillUnits(NamedTuple):

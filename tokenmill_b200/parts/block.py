@@ -136,6 +136,24 @@ class ParallelShiftBlock:
         return Pending(branch=mixed, branch2=fed, scale=self.mult)
 
 
+class ParallelBlock:
+    """``x <- x + (mixer(h) + feed_forward(h))`` with ``h = norm(x)``: ONE norm, and both sublayers read its output. Neither
+    result is added where it is produced: the next norm takes both as two branches and adds their sum while it reads
+    the row (a norm that takes ``branch`` and ``branch2``). The feed-forward may be absent."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm=None):
+        if feed_forward_norm is not None:
+            raise ValueError("a parallel block has one norm; its feed-forward reads the mixer's")
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, None
+
+    def forward(self, resid: torch.Tensor, pending: Pending, step: StepInputs, cache: LayerCache) -> Pending:
+        h = self.mixer_norm.forward(resid, **pending.kwargs())
+        mixed = self.mixer.forward(h, step, cache)
+        fed = self.feed_forward.forward(h, step) if self.feed_forward is not None else None
+        return Pending(branch=mixed, branch2=fed)
+
+
 class ConvGatedBlock:
     """Pre-norm block with two additions. Each sublayer reads its normed input h through a short causal convolution
     over time, ``h + conv(h)`` with ``conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j)`` per channel (tensors ``canon1`` and
@@ -278,6 +296,7 @@ class HyperConnectionBlock:
 
 
 register_block("conv_gated", ConvGatedBlock)
+register_block("parallel", ParallelBlock)
 register_block("hyper_connections", HyperConnectionBlock)
 register_block("pre_norm", PreNormBlock)
 register_block("parallel_shift", ParallelShiftBlock)

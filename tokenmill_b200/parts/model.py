@@ -202,7 +202,7 @@ class DecoderModel:
         parts = [p for blk in self.blocks for p in (blk, blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm)
                  if p is not None]
         if self.dtype != torch.bfloat16 or s.embedding_scale != 1.0 or s.streams != 1 or s.position_table_name is not None or \
-                s.logit_softcap or not all(hasattr(p, "emit") for p in parts + [self.final_norm]):
+                s.logit_softcap or s.logit_scale != 1.0 or not all(hasattr(p, "emit") for p in parts + [self.final_norm]):
             return None
         b = ProgramBuilder(self.device, self.dtype)
         try:
@@ -236,4 +236,6 @@ class DecoderModel:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.device)
         hidden = self.final_norm.forward(resid, rows=step.want_rows, **pending.kwargs())
         logits = ops.linear(hidden, self.output_weight, out_dtype=torch.float32)
-        return ops.softcap_(logits, s.logit_softcap) if s.logit_softcap else logits
+        if s.logit_softcap or s.logit_scale != 1.0:
+            return ops.softcap_(logits, s.logit_softcap, s.logit_scale)
+        return logits

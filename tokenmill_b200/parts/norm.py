@@ -131,15 +131,15 @@ class DynamicTanhNorm:
     It reads a residual of one or several streams (``streams`` copies of the row side by side, ``resid`` [T, streams * H]):
     on the way it takes in the previous sublayer's result, ``x_t <- sum_s stream_mix[s, t] x_s + stream_out[t] y`` (one
     stream without a mix: ``x += y``), with ``y = branch + row_scale * branch2``; or starts every stream as
-    ``table[ids] + pos_table[positions]``; then norms ``u = sum_s stream_in[s] x_s`` (no ``stream_in``: the sum of the
+    ``table[ids] * table_scale + pos_table[positions]``; then norms ``u = sum_s stream_in[s] x_s`` (no ``stream_in``: the sum of the
     streams, which is what a model's last norm reads). ``kind="rms"`` keeps all of that with an RMS norm (weight only)."""
 
     def __init__(self, *, hidden_size: int, streams: int = 1, kind: str = "dyt", eps: float = 0.0,
-                 names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
+                 names: dict[str, str] | None = None, library: str = "streams", dtype: torch.dtype, device: torch.device):
         if kind not in ops.STREAM_NORMS or not 1 <= streams <= ops.MAX_STREAMS:
             raise ValueError(f"norm kinds {sorted(ops.STREAM_NORMS)} over 1 to {ops.MAX_STREAMS} streams are built, got "
                              f"{kind!r} over {streams}")
-        lib.prefer("streams")
+        lib.prefer(library)      # the kernel library a model of such norms runs from (kernels/build.py)
         self.hidden_size, self.streams, self.kind, self.eps = hidden_size, int(streams), kind, float(eps)
         self.dtype, self.device = dtype, device
         self.names = {"weight": "", "bias": "b", "alpha": "alpha", **(names or {})}
@@ -163,15 +163,19 @@ class DynamicTanhNorm:
                 partials: torch.Tensor | None = None, ids: torch.Tensor | None = None, table: torch.Tensor | None = None,
                 positions: torch.Tensor | None = None, pos_table: torch.Tensor | None = None,
                 rows: torch.Tensor | None = None, stream_mix: torch.Tensor | None = None,
-                stream_out: torch.Tensor | None = None, stream_in: torch.Tensor | None = None) -> torch.Tensor:
+                stream_out: torch.Tensor | None = None, stream_in: torch.Tensor | None = None,
+                table_scale: float = 1.0, scale: float = 1.0) -> torch.Tensor:
         if partials is not None:
             raise NotImplementedError("this norm takes branch outputs, not partial products")
+        if scale != 1.0:
+            raise NotImplementedError("this norm adds branch outputs as they are")
         n = rows.numel() if rows is not None else resid.shape[0]
         if out is None:
             out = torch.empty((n, self.hidden_size), dtype=self.dtype, device=resid.device)
         return ops.stream_norm(resid, self.streams, out, kind=self.kind, weight=self.weight, bias=self.bias, alpha=self.alpha,
                                eps=self.eps, ids=ids, table=table, positions=positions, pos_table=pos_table, branch=branch,
-                               branch2=branch2, row_scale=row_scale, mix=stream_mix, out_w=stream_out, in_w=stream_in, rows=rows)
+                               branch2=branch2, row_scale=row_scale, mix=stream_mix, out_w=stream_out, in_w=stream_in, rows=rows,
+                               table_scale=table_scale)
 
 
 register_norm("dyt", DynamicTanhNorm)

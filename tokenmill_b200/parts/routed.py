@@ -13,6 +13,14 @@ second product sums the chosen experts with their weights in its 32-bit accumula
 tensors, whose result is the input h itself. Scores are a softmax over ALL router outputs; the choice is made by score +
 ``correction`` (a learned vector that does not enter the weights), among the best ``keep`` of ``groups`` equal groups of
 neighbouring outputs (a group's score: its largest choice score); the weights are the chosen scores divided by their sum.
+
+``InputScaledExperts``: E small gated feed-forwards ``W_down (silu(W_gate x) * (W_up x))`` of which each token uses
+``top``, chosen by the largest router logits (32-bit). A chosen expert's weight is the sigmoid of its logit, not
+renormalized, and it multiplies the expert's INPUT: the output is the sum of expert(w h). Optionally a shared expert of
+the same form runs for every token and is added, times sigmoid(W_sg h), one number per token. The products W_gate h
+and W_up h of all experts (and of the shared one) run as one matrix product on h itself; the activation kernel forms
+silu(w g) * (w u) for the chosen experts and exact zeros for the others, and one down product over [E F + shared]
+sums them. The router and the shared expert's gate are one 32-bit product.
 """
 
 from __future__ import annotations
@@ -164,6 +172,72 @@ class ChoiceRoutedExperts:
         return ops.add_scaled_rows(out, x2, id_w)
 
 
+class InputScaledExperts:
+    def __init__(self, *, hidden_size: int, expert_size: int, num_experts: int, top: int, shared_size: int = 0,
+                 shared_gate: bool = True, names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
+        if not 1 <= top <= num_experts:
+            raise ValueError(f"top ({top}) must lie between 1 and the number of experts ({num_experts})")
+        if shared_size < 0:
+            raise ValueError("the shared expert has no negative size")
+        self.hidden_size, self.F, self.E, self.top, self.Fs = hidden_size, expert_size, num_experts, top, int(shared_size)
+        self.gated = bool(shared_gate) and self.Fs > 0
+        self.dtype, self.device = dtype, device
+        # {e} is the expert's number
+        self.names = {"router": "router", "gate": "e{e}.gate", "up": "e{e}.up", "down": "e{e}.down",
+                      "shared_gate": "shared.gate", "shared_up": "shared.up", "shared_down": "shared.down",
+                      "shared_weight": "shared.sg", **(names or {})}
+        self.w_router = self.w_router_low = self.w_gate_up = self.w_down = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        H, F, n = self.hidden_size, self.F, self.names
+        specs = []
+        for e in range(self.E):
+            specs += [WeightSpec(n["gate"].format(e=e), (F, H), init=("normal", 0.05)),
+                      WeightSpec(n["up"].format(e=e), (F, H), init=("normal", 0.05)),
+                      WeightSpec(n["down"].format(e=e), (H, F), init=("normal", 0.05))]
+        specs.append(WeightSpec(n["router"], (self.E, H), dtype="float32", init=("normal", 0.3)))
+        if self.Fs:
+            specs += [WeightSpec(n["shared_gate"], (self.Fs, H), init=("normal", 0.05)),
+                      WeightSpec(n["shared_up"], (self.Fs, H), init=("normal", 0.05)),
+                      WeightSpec(n["shared_down"], (H, self.Fs), init=("normal", 0.05))]
+        if self.gated:
+            specs.append(WeightSpec(n["shared_weight"], (1, H), dtype="float32", init=("normal", 0.3)))
+        return specs
+
+    def activation_bytes(self, n_tokens: int) -> int:
+        elt = 4 if self.dtype == torch.float32 else 2
+        return n_tokens * ((3 * (self.E * self.F + self.Fs) + self.hidden_size) * elt + 12 * (self.E + 1))
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        n = self.names
+        # the router's rows, then the shared expert's gate as one more row: one 32-bit product serves both
+        rows = [tensors[n["router"]]] + ([tensors[n["shared_weight"]].reshape(1, -1)] if self.gated else [])
+        self.w_router = torch.cat(rows, dim=0).contiguous()
+        low = self.w_router.to(torch.bfloat16)
+        self.w_router_low = low if self.dtype == torch.bfloat16 and bool((low.float() == self.w_router).all()) else None
+        parts = [t for e in range(self.E) for t in (tensors[n["gate"].format(e=e)], tensors[n["up"].format(e=e)])]
+        downs = [tensors[n["down"].format(e=e)] for e in range(self.E)]
+        if self.Fs:
+            parts += [tensors[n["shared_gate"]], tensors[n["shared_up"]]]
+            downs.append(tensors[n["shared_down"]])
+        self.w_gate_up = torch.cat(parts, dim=0).contiguous()                # [E * 2 F + 2 Fs, H]
+        self.w_down = torch.cat(downs, dim=1).contiguous()                   # [H, E F + Fs]
+
+    def route(self, x: torch.Tensor):
+        """(chosen experts [T, top] int32, their weights [T, top], dense weights [T, E] float32, the logits [T, E (+ 1)])."""
+        logits = ops.router_logits(x, self.w_router, self.w_router_low)
+        return (*ops.moe_topk(logits, self.E, self.top, "sigmoid"), logits)
+
+    def forward(self, x: torch.Tensor, step: StepInputs | None = None) -> torch.Tensor:
+        T = x.shape[0]
+        _idx, _w, dense, logits = self.route(x)
+        gu = ops.linear(x, self.w_gate_up)
+        act = torch.empty((T, self.E * self.F + self.Fs), dtype=self.dtype, device=x.device)
+        ops.glu_routed_in(gu, dense, act, self.E, self.F, self.Fs, logits[:, self.E] if self.gated else None)
+        return ops.linear(act, self.w_down)
+
+
+register_feed_forward("routed_input_scaled", InputScaledExperts)
 register_feed_forward("routed_choice", ChoiceRoutedExperts)
 register_feed_forward("relu2", SquaredReluFeedForward)
 register_feed_forward("routed_experts", RoutedExperts)

@@ -14,7 +14,16 @@
   projection (``value_gate``);
 * a query temperature: q is multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)`` at position p (``q_temp``);
 * no keys and values of its own (``shares_kv``): the layer has no k and v tensors and reads the cache of another
-  layer with the same head counts and sizes (the run order's ``cache_of``), with its own queries, mask and gate.
+  layer with the same head counts and sizes (the run order's ``cache_of``), with its own queries, mask and gate;
+* biases of the q, k and v projections (``bias``: tensors ``<q>.b`` and so on), added to the product's 32-bit result;
+* a short causal convolution over time on every channel of q, k and v, directly after the projection (``conv_taps`` >= 1:
+  tensors ``<q>.conv`` [channels, taps], the last tap weighing the current token; a request's last taps - 1 projected
+  rows are per-request state of the mixer; 0: none);
+* ``qk_norm="head"``: every head of q and of k divided by its own root mean square, without weights;
+* talking heads (``talk``: tensor [heads, heads]): after the softmax the heads' weights are mixed, weight_h <- sum_g
+  talk[h, g] weight_g, and head h applies its mixed weights to the values of its own key/value head. The softmax and the
+  product with the values are linear in between, so the kernel applies every head's own weights to the values of each
+  value head ([T, heads, kv_heads, vdim] in 32-bit) and a small kernel mixes those results.
 
 Projections q, k, v (and g) are held as one matrix whose product keeps its 32-bit accumulator; one kernel norms,
 rotates and writes the token's cache row ``[k | v]`` (a paged cache of one plane whose row holds all key heads, then
@@ -43,6 +52,7 @@ class SinkWindowAttention:
                  position: PartSpec | None, rot_dims: int = 0, window: int | None = None, keep_first: int = 0,
                  softcap: float = 0.0, sink: bool = True, qk_norm: bool = True, head_gate: bool = True, eps: float = 1e-6,
                  value_gate: bool = False, q_temp: tuple[float, int] | None = None, shares_kv: bool = False,
+                 bias: bool = False, conv_taps: int = 0, talk: bool = False,
                  names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
         if num_heads % num_kv_heads:
             raise ValueError(f"heads ({num_heads}) must be a multiple of kv heads ({num_kv_heads})")
@@ -51,7 +61,17 @@ class SinkWindowAttention:
         self.hidden_size, self.nh, self.nkv, self.d, self.dv = hidden_size, num_heads, num_kv_heads, head_dim, value_dim
         self.scale, self.softcap, self.eps = float(scale), float(softcap or 0.0), float(eps)
         self.window, self.keep_first = int(window) if window else 0, int(keep_first or 0)
-        self.sink, self.qk_norm, self.head_gate = bool(sink), bool(qk_norm), bool(head_gate)
+        if qk_norm not in (True, False, "head"):
+            raise ValueError(f"qk_norm is False, True (whole projections, weights) or 'head', got {qk_norm!r}")
+        self.head_norm = qk_norm == "head"
+        self.bias, self.taps, self.talk = bool(bias), int(conv_taps), bool(talk)
+        if not 0 <= self.taps <= 16:
+            raise ValueError(f"convolutions of up to 16 taps are built, got {conv_taps}")
+        if (self.taps or self.bias) and shares_kv:
+            raise ValueError("a layer that reads another layer's keys has no biases and no convolution")
+        if (self.talk or self.taps or self.bias) and (head_gate or value_gate):
+            raise ValueError("mixed heads, biases and convolved projections are built without an output gate")
+        self.sink, self.qk_norm, self.head_gate = bool(sink), qk_norm is True, bool(head_gate)
         self.value_gate, self.shares_kv = bool(value_gate), bool(shares_kv)
         if self.value_gate and self.head_gate:
             raise ValueError("the output gate has one number per head or one per output number, not both")
@@ -66,7 +86,8 @@ class SinkWindowAttention:
             raise ValueError(f"rot_dims ({self.rot_dims}) must be even and at most head_dim ({head_dim})")
         self.dtype, self.device = dtype, device
         self.names = {"q": "q", "k": "k", "v": "v", "q_norm": "q.norm", "k_norm": "k.norm", "g": "g", "o": "o",
-                      **(names or {})}
+                      "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b", "q_conv": "q.conv", "k_conv": "k.conv",
+                      "v_conv": "v.conv", "talk": "talk", **(names or {})}
         self.q_size, self.k_size, self.v_size = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
         self.gate_cols = num_heads if self.head_gate else num_heads * value_dim if self.value_gate else 0
         self.proj_width = self.q_size + (0 if self.shares_kv else self.k_size + self.v_size) + self.gate_cols
@@ -74,7 +95,9 @@ class SinkWindowAttention:
         # path): the shape-generic kernel on CUDA cores, 32 rows a tile
         self.tensor_cores = ops.sink_attention_tc_ok(dtype, head_dim, value_dim) and self.scale > 0
         self.tile_rows = ops.SINK_TC_TILE_ROWS if self.tensor_cores else ops.SINK_TILE_ROWS
+        self.qkv_width = self.q_size + self.k_size + self.v_size
         self.w_in = self.w_o = self.g_q = self.g_k = self.cos = self.sin = None
+        self.b_in = self.w_conv = self.w_talk = None
 
     # --- declarations -----------------------------------------------------------------------------------------
 
@@ -89,6 +112,14 @@ class SinkWindowAttention:
                       WeightSpec(n["k_norm"], (self.k_size,), dtype="float32", init=("ones_plus_normal", 0.1))]
         if self.gate_cols:
             specs.append(WeightSpec(n["g"], (self.gate_cols, W), init=("normal", 0.05)))
+        sizes = (("q", self.q_size), ("k", self.k_size), ("v", self.v_size))
+        if self.bias:
+            specs += [WeightSpec(n[f"{x}_bias"], (size,), dtype="float32", init=("normal", 0.1)) for x, size in sizes]
+        if self.taps:
+            specs += [WeightSpec(n[f"{x}_conv"], (size, self.taps), dtype="float32", init=("normal", 0.3, 1.0 / self.taps))
+                      for x, size in sizes]
+        if self.talk:
+            specs.append(WeightSpec(n["talk"], (self.nh, self.nh), dtype="float32", init=("normal", 0.3, 1.0 / self.nh)))
         specs.append(WeightSpec(n["o"], (W, self.nh * self.dv), init=("normal", 0.05)))
         return specs
 
@@ -97,7 +128,7 @@ class SinkWindowAttention:
                            keep_first=self.keep_first if self.window else 0)
 
     def state_need(self) -> StateNeed | None:
-        return None
+        return StateNeed(((self.taps - 1) * self.qkv_width,), "float32") if self.taps > 1 else None
 
     def max_positions(self) -> int | None:
         return part_max_positions(self.position) if self.position is not None else None
@@ -118,6 +149,14 @@ class SinkWindowAttention:
         self.w_o = tensors[n["o"]]
         if self.qk_norm:
             self.g_q, self.g_k = tensors[n["q_norm"]], tensors[n["k_norm"]]
+        if self.bias:
+            self.b_in = torch.cat([tensors[n[f"{x}_bias"]] for x in "qkv"]).contiguous()
+        if self.taps:
+            self.w_conv = torch.cat([tensors[n[f"{x}_conv"]] for x in "qkv"], dim=0).contiguous()
+        elif self.bias:
+            self.w_conv = torch.ones((self.qkv_width, 1), dtype=torch.float32, device=self.device)
+        if self.talk:
+            self.w_talk = tensors[n["talk"]].contiguous()
         if self.position is not None:
             self.cos, self.sin = self.position.tables(self.device)
         else:       # no rotation: tables of no columns
@@ -130,7 +169,7 @@ class SinkWindowAttention:
     # --- per-step work list -----------------------------------------------------------------------------------
 
     def metadata_key(self):
-        return ("sink_attention", self.nh // self.nkv, self.tile_rows)
+        return ("sink_attention", self.nh // self.nkv, self.tile_rows, self.nkv if self.talk else 0)
 
     def step_metadata(self, shape: StepShape) -> StepMetadata:
         """Row tiles of the attention kernel: ``tile_rows`` consecutive (token, head in group) rows of one request each."""
@@ -145,7 +184,8 @@ class SinkWindowAttention:
         if self.tensor_cores and n_tiles:
             longest = shape.max_kv_len if shape.for_graph else int((shape.starts.astype(np.int64) + shape.q_lens).max())
             keys = min(longest, self.window + self.keep_first + rows) if self.window else longest
-            splits = max(1, min((keys // 64 + 1) // 2, SPLIT_BLOCKS // (n_tiles * self.nkv), MAX_SPLITS))
+            blocks = n_tiles * self.nkv * (self.nkv if self.talk else 1)
+            splits = max(1, min((keys // 64 + 1) // 2, SPLIT_BLOCKS // blocks, MAX_SPLITS))
         return StepMetadata({"tile_seq": tile_seq, "tile_row0": tile_row0}, {"n_tiles": n_tiles, "n_splits": splits},
                             constant_in_graph=True)
 
@@ -158,6 +198,12 @@ class SinkWindowAttention:
         """``proj`` [T, proj_width] float32 (a view of a wider product is fine): this mixer's columns [q | k | v | g]
         ([q | g] for a layer that reads another layer's keys and values)."""
         T, dev = proj.shape[0], proj.device
+        if self.taps or self.bias:      # q, k and v through the convolution (the biases enter on the way); what follows
+            # reads that. Biases alone: a convolution of one tap with weights of one, which carries nothing.
+            conv = torch.empty((T, self.qkv_width), dtype=torch.float32, device=dev)
+            state = cache.state if self.taps > 1 else torch.empty((1, 0), dtype=torch.float32, device=dev)
+            proj = ops.short_conv_state(proj, 0, self.w_conv, self.b_in, state, cache.state_off if self.taps > 1 else 0,
+                                        step.cu_q, step.seq_of_token, step.state_slots, conv)
         q = torch.empty((T, self.q_size), dtype=self.dtype, device=dev)
         gate = torch.empty((T, self.gate_cols), dtype=torch.float32, device=dev) if self.gate_cols else None
         rows = cache.k.view(-1, self.k_size + self.v_size)
@@ -167,18 +213,21 @@ class SinkWindowAttention:
                                wq=self.g_q, wk=self.g_k, eps=self.eps, positions=step.positions, cos=self.cos, sin=self.sin,
                                slot_map=step.slot_maps[cache.group] if cache.writes else None, q_out=q,
                                cache=rows if cache.writes else None, gate_out=gate, has_kv=not self.shares_kv,
-                               q_temp=self.q_temp)
+                               q_temp=self.q_temp, head_norm=self.head_norm)
         meta = step.meta[self.metadata_key()]
         heads = torch.empty((T, self.nh * self.dv), dtype=self.dtype, device=dev)
+        cross = torch.empty((T, self.nh * self.nkv * self.dv), dtype=torch.float32, device=dev) if self.talk else None
         splits, part = meta.host["n_splits"], None
         if splits > 1:
-            part = step.workspace.get("sink_attention_part", meta.host["n_tiles"] * self.nkv * splits * self.tile_rows *
-                                      (self.dv + 2), torch.float32)
+            part = step.workspace.get("sink_attention_part", meta.host["n_tiles"] * self.nkv * (self.nkv if self.talk else 1) *
+                                      splits * self.tile_rows * (self.dv + 2), torch.float32)
         ops.sink_attention(q, cache.k, step.block_tables[cache.group], step.cu_q, step.kv_before, meta.arrays["tile_seq"],
                            meta.arrays["tile_row0"], meta.host["n_tiles"], gate, heads, heads=self.nh, kv_heads=self.nkv,
                            dim=self.d, vdim=self.dv, scale=self.scale, softcap=self.softcap, window=self.window,
                            keep_first=self.keep_first, sink=self.sink, tensor_cores=self.tensor_cores, n_splits=splits,
-                           part=part)
+                           part=part, cross_out=cross)
+        if self.talk:
+            ops.talk_mix(cross, self.w_talk, heads, self.nh, self.nkv, self.dv)
         return ops.linear(heads, self.w_o)
 
 

@@ -19,8 +19,8 @@ class WeightSpec:
            "float32" - held in 32-bit whatever the run's dtype (norm weights, biases: small vectors
                        whose arithmetic is 32-bit in the kernels);
            "int32"   - an integer table.
-    init:  how the random-weights writer fills it: ("normal", std), ("normal", std, mean) or
-           ("ones_plus_normal", std).
+    init:  how the random-weights writer fills it: ("normal", std), ("normal", std, mean),
+           ("ones_plus_normal", std) or ("uniform", low, high).
     An empty ``name`` stands for the part's prefix itself (a part whose one tensor has no name of its own).
     """
 
@@ -115,6 +115,7 @@ class ModelSpec:
     streams: int = 1                              # copies of the residual stream a token carries (hyper-connections);
                                                   # the blocks say how they are read and written
     logit_softcap: float = 0.0                    # logits <- cap * tanh(logits / cap); 0: none
+    logit_scale: float = 1.0                      # the logits are multiplied by this first (before the cap)
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -30,6 +30,10 @@ def random_tensors(model: DecoderModel, seed: int, store_dtype: torch.dtype) -> 
         if spec.dtype == "int32":
             out[spec.name] = torch.zeros(spec.shape, dtype=torch.int32)
             continue
+        if kind == "uniform":           # ("uniform", low, high)
+            low, high = spec.init[1], spec.init[2]
+            out[spec.name] = (torch.rand(spec.shape, dtype=torch.float32, generator=gen) * (high - low) + low).to(store_dtype)
+            continue
         t = torch.empty(spec.shape, dtype=torch.float32).normal_(0.0, std, generator=gen) + mean
         if kind == "ones_plus_normal":
             t += 1.0
