@@ -252,13 +252,77 @@ def _dibizen_named(name: str) -> dict | None:
     return None
 
 
+def gofezen_pair(*, heads, kv_heads, dim, vdim, scale, conv, window, r_heads, r_qk_heads, r_dim, r_vdim, r_conv,
+                 left_scale=1.0, right_scale=1.0) -> dict:
+    """The ``mixer`` entry of a Gofezen layer of type "parallel": windowed attention (left) beside the gated delta rule
+    (right; its ``kv_heads`` counts its q/k heads)."""
+    return {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": float(scale), "conv": conv,
+                     "mask": {"size": window}},
+            "right": {"heads": r_heads, "kv_heads": r_qk_heads, "dim": r_dim, "vdim": r_vdim, "conv": r_conv},
+            "left_scale": float(left_scale), "right_scale": float(right_scale)}
+
+
+def gofezen_hgrn2(*, heads, dim, vdim) -> dict:
+    """The ``mixer`` entry of a Gofezen layer of type "hgrn2"."""
+    return {"heads": heads, "dim": dim, "vdim": vdim}
+
+
+def gofezen_moe(*, experts, top, ff, shared=None) -> dict:
+    """The ``mlp`` entry of a Gofezen layer with experts; ``shared``: the shared expert's size or None."""
+    out = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    if shared:
+        out["shared"] = {"ff": shared}
+    return out
+
+
+def gofezen_config(*, vocab, width, layers, eps=1e-6, max_positions=512, embedding_scale=1.0, logit_scale=1.0,
+                   logit_softcap=30.0) -> dict:
+    """config.json of a Gofezen model. ``layers``: (type, mixer entry, mlp entry or None); a dense feed-forward is
+    {"kind": "dense", "ff": n}."""
+    return {"architecture": "Gofezen", "vocab": vocab, "width": width, "norm": {"eps": eps}, "max_positions": max_positions,
+            "embedding": {"scale": float(embedding_scale)}, "logit_scale": float(logit_scale),
+            "logit_softcap": float(logit_softcap),
+            "layers": [{"type": kind, "mixer": mixer, "mlp": mlp} for kind, mixer, mlp in layers]}
+
+
+def _gofezen_named(name: str) -> dict | None:
+    P, R, E = gofezen_pair, gofezen_hgrn2, gofezen_moe
+    dense = lambda ff: {"kind": "dense", "ff": ff}
+    if name == "gofezen-tiny-a":     # two pairs of unlike sizes; layers without feed-forward; one tap; top 2 and top 1
+        return gofezen_config(vocab=173, width=48, max_positions=300, embedding_scale=6.9, logit_scale=0.7, logit_softcap=8.0, layers=[
+            ("parallel", P(heads=4, kv_heads=2, dim=12, vdim=20, scale=0.3, conv=3, window=24, r_heads=4, r_qk_heads=2, r_dim=16,
+                           r_vdim=12, r_conv=4, left_scale=1.3, right_scale=0.8), E(experts=6, top=2, ff=24, shared=16)),
+            ("hgrn2", R(heads=3, dim=10, vdim=14), dense(64)),
+            ("hgrn2", R(heads=2, dim=24, vdim=8), None),
+            ("parallel", P(heads=6, kv_heads=3, dim=8, vdim=8, scale=0.5, conv=2, window=37, r_heads=3, r_qk_heads=3, r_dim=20,
+                           r_vdim=28, r_conv=1, left_scale=0.6, right_scale=1.5), E(experts=4, top=1, ff=20))])
+    if name == "gofezen-tiny-b":     # every head its own keys / one key head for all; no cap, no scales; a window no request fills
+        return gofezen_config(vocab=300, width=80, eps=1e-5, max_positions=400, logit_softcap=0.0, layers=[
+            ("hgrn2", R(heads=1, dim=40, vdim=24), E(experts=3, top=3, ff=32, shared=8)),
+            ("parallel", P(heads=5, kv_heads=5, dim=8, vdim=16, scale=0.35, conv=1, window=1000, r_heads=2, r_qk_heads=1, r_dim=40,
+                           r_vdim=20, r_conv=2), dense(96)),
+            ("parallel", P(heads=3, kv_heads=1, dim=16, vdim=8, scale=0.25, conv=5, window=9, r_heads=5, r_qk_heads=5, r_dim=8,
+                           r_vdim=8, r_conv=3, left_scale=2.0, right_scale=0.5), None)])
+    if name == "gofezen-tiny-c":     # head sizes the tensor-core attention takes (bfloat16); wide memories
+        return gofezen_config(vocab=210, width=64, max_positions=350, embedding_scale=8.0, logit_scale=0.5, layers=[
+            ("parallel", P(heads=8, kv_heads=2, dim=64, vdim=32, scale=0.125, conv=4, window=70, r_heads=4, r_qk_heads=2, r_dim=64,
+                           r_vdim=32, r_conv=4, left_scale=1.1, right_scale=0.9), E(experts=7, top=2, ff=16, shared=24)),
+            ("hgrn2", R(heads=2, dim=70, vdim=16), E(experts=5, top=1, ff=24)),
+            ("parallel", P(heads=4, kv_heads=4, dim=32, vdim=64, scale=0.18, conv=2, window=33, r_heads=2, r_qk_heads=2, r_dim=130,
+                           r_vdim=24, r_conv=3), dense(80)),
+            ("hgrn2", R(heads=4, dim=16, vdim=40), None)])
+    return None
+
+
 def named_config(name: str) -> dict:
-    cfg = _kutirax_named(name.lower()) or _bobunex_named(name.lower()) or _dibizen_named(name.lower())
+    cfg = _kutirax_named(name.lower()) or _bobunex_named(name.lower()) or _dibizen_named(name.lower()) or \
+        _gofezen_named(name.lower())
     if cfg is not None:
         return cfg
     try:
         return qwen2_config(**NAMED_SIZES[name.lower()])
     except KeyError:
         known = sorted(NAMED_SIZES) + ["kutirax-tiny-a", "kutirax-tiny-b", "kutirax-tiny-c", "bobunex-tiny-a", "bobunex-tiny-b",
-                                       "bobunex-tiny-c", "bobunex-tiny-d", "dibizen-tiny-a", "dibizen-tiny-b", "dibizen-tiny-c"]
+                                       "bobunex-tiny-c", "bobunex-tiny-d", "dibizen-tiny-a", "dibizen-tiny-b", "dibizen-tiny-c",
+                                       "gofezen-tiny-a", "gofezen-tiny-b", "gofezen-tiny-c"]
         raise ValueError(f"unknown size name {name!r}; known: {known}") from None
