@@ -27,10 +27,11 @@ chunked prefill with a 2,048-token budget; ``7b-prefix``: Qwen2.5-7B sizes, cont
 4,096-token prompts that share their first 1,024 tokens, 512 new tokens, prefix caching, a pool too small for
 all of them so that requests are preempted.
 
-``--design kutirax|bobunex|dibizen [--design-sizes s|m] [--kernels]`` measures another design (Kutirax: latent attention with a window,
+``--design kutirax|bobunex|dibizen|gofezen [--design-sizes s|m] [--kernels]`` measures another design (Kutirax: latent attention with a window,
 state-space layers, experts; Bobunex: windowed attention with a sink beside a matrix memory; Dibizen: selective scan, attention, linear
-attention with a decay and experts chosen among groups, over two residual streams) beside Qwen2 (Dibizen: beside Kutirax, the closest
-of the models) at the same width, depth and vocabulary: one 2,048-token prompt and decode
+attention with a decay and experts chosen among groups, over two residual streams; Gofezen: windowed attention with mixed heads
+beside the gated delta rule, forget-gate memories, experts weighted on their input) beside Qwen2 (Dibizen: beside Kutirax, Gofezen:
+beside Dibizen, the closest of the models) at the same width, depth and vocabulary: one 2,048-token prompt and decode
 steps of 8 and 32 requests, and with ``--kernels`` the device time by kernel name of one step of each kind.
 
 The engine runs on one GPU: for --gpus N > 1 a line says so and the exit code is 2.
@@ -728,6 +729,9 @@ DESIGN_SIZES = {
               dibizen=dict(attention=dict(heads=8, kv_heads=2, dim=128, vdim=128, scale=128 ** -0.5, q_temp=(0.1, 512)),
                            lightning=dict(heads=8, dim=128, vdim=128), mamba=dict(inner=2048, state=16, dt_rank=64, conv=4),
                            moe=dict(experts=14, top=2, ff=1024, identity=2, groups=(4, 2))),
+              gofezen=dict(pair=dict(heads=8, kv_heads=2, dim=128, vdim=128, scale=128 ** -0.5, conv=3, window=512, r_heads=8,
+                                     r_qk_heads=4, r_dim=128, r_vdim=128, r_conv=4, left_scale=1.2, right_scale=1.1),
+                           hgrn2=dict(heads=8, dim=128, vdim=128), dense=2816, moe=dict(experts=14, top=2, ff=1024, shared=1024)),
               qwen=dict(num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=2816)),
     "m": dict(width=2048,
               latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=512, window=1024),
@@ -739,6 +743,9 @@ DESIGN_SIZES = {
               dibizen=dict(attention=dict(heads=16, kv_heads=2, dim=128, vdim=128, scale=128 ** -0.5, q_temp=(0.1, 512)),
                            lightning=dict(heads=16, dim=128, vdim=128), mamba=dict(inner=4096, state=16, dt_rank=128, conv=4),
                            moe=dict(experts=30, top=4, ff=1024, identity=2, groups=(8, 4))),
+              gofezen=dict(pair=dict(heads=16, kv_heads=2, dim=128, vdim=128, scale=128 ** -0.5, conv=3, window=1024, r_heads=16,
+                                     r_qk_heads=8, r_dim=128, r_vdim=128, r_conv=4, left_scale=1.2, right_scale=1.1),
+                           hgrn2=dict(heads=16, dim=128, vdim=128), dense=5632, moe=dict(experts=30, top=4, ff=1024, shared=2048)),
               qwen=dict(num_attention_heads=16, num_key_value_heads=2, head_dim=128, intermediate_size=5632)),
 }
 
@@ -749,17 +756,22 @@ def design_model_dirs(size: str, vocab: int, design: str = "kutirax"):
     Bobunex: four layers of windowed attention beside a matrix memory, with a gated gelu feed-forward. Both beside Qwen2.
     Dibizen: selective scan, attention, linear attention with a decay, attention on the second layer's keys, each with
     experts chosen among groups, over two residual streams; beside Kutirax, the closest existing model (state-space layers,
-    attention and routed experts of the same count, size and top)."""
+    attention and routed experts of the same count, size and top). Gofezen: a pair (windowed attention with mixed heads
+    beside the gated delta rule) with a dense feed-forward, two forget-gate memories and another pair, each with experts
+    weighted on their input and a shared expert; beside Dibizen, the closest existing model (recurrent layers with state
+    slots beside attention with pages, experts computed densely, a learned position table, capped logits)."""
     from tokenmill_b200.weights import qwen2_config, write_random_model
     from tokenmill_b200.weights.random_init import (bobunex_attention, bobunex_config, bobunex_memory, dibizen_attention,
                                                     dibizen_config, dibizen_lightning, dibizen_mamba, dibizen_moe,
+                                                    gofezen_config, gofezen_hgrn2, gofezen_moe, gofezen_pair,
                                                     kutirax_config, kutirax_latent, kutirax_mamba)
     z = DESIGN_SIZES[size]
     lat, mam, moe = kutirax_latent(**z["latent"]), kutirax_mamba(**z["mamba"]), ("moe", *z["moe"])
     kutirax = kutirax_config(vocab=vocab, width=z["width"], eps=1e-5, residual_mult=0.5, layers=[
         ("mamba2", mam, ("dense", z["dense"])), ("latent_attention", lat, moe), ("latent_attention", lat, moe),
         ("mamba2", mam, moe)])
-    if design == "dibizen":
+    beside_cfg = None
+    if design in ("dibizen", "gofezen"):
         d = z["dibizen"]
         nh = d["lightning"]["heads"]
         e = dibizen_moe(**d["moe"])
@@ -767,6 +779,15 @@ def design_model_dirs(size: str, vocab: int, design: str = "kutirax"):
             ("mamba1", dibizen_mamba(**d["mamba"]), e), ("attention", dibizen_attention(**d["attention"]), e),
             ("lightning", dibizen_lightning(**d["lightning"], decay=[1.0 - 2.0 ** -(5 + 5 * h / nh) for h in range(nh)]), e),
             ("attention", dibizen_attention(**d["attention"], kv_from=1), e)])
+        beside_cfg = ("kutirax", kutirax)
+        if design == "gofezen":
+            g = z["gofezen"]
+            e, pair, mem = gofezen_moe(**g["moe"]), gofezen_pair(**g["pair"]), gofezen_hgrn2(**g["hgrn2"])
+            beside_cfg = ("dibizen", kcfg)
+            kcfg = gofezen_config(vocab=vocab, width=z["width"], eps=1e-6, max_positions=4096, embedding_scale=z["width"] ** 0.5,
+                                  logit_scale=0.5, logit_softcap=30.0, layers=[
+                                      ("parallel", pair, {"kind": "dense", "ff": g["dense"]}), ("hgrn2", mem, e), ("hgrn2", mem, e),
+                                      ("parallel", pair, e)])
     elif design == "bobunex":
         b = z["bobunex"]
         kcfg = bobunex_config(vocab=vocab, width=z["width"], eps=1e-6, embedding_scale=8.0, taps=b["taps"], layers=[
@@ -776,7 +797,7 @@ def design_model_dirs(size: str, vocab: int, design: str = "kutirax"):
     qcfg = qwen2_config(vocab_size=vocab, hidden_size=z["width"], num_hidden_layers=4, rope_theta=1000000.0,
                         rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=32768, **z["qwen"])
     dirs = []
-    for name, cfg in ((design, kcfg), ("kutirax", kutirax) if design == "dibizen" else ("qwen2", qcfg)):
+    for name, cfg in ((design, kcfg), beside_cfg or ("qwen2", qcfg)):
         tmp = tempfile.TemporaryDirectory(prefix=f"tokenmill_bench_{name}_")
         t0 = time.time()
         write_random_model(tmp.name, cfg, seed=0)
@@ -833,7 +854,7 @@ def run_design(args) -> dict:
     global NEW_TOKENS
     vocab = SIZES["vocab_size"]
     kdir, qdir, z = design_model_dirs(args.design_sizes, vocab, args.design)
-    beside = "kutirax" if args.design == "dibizen" else "qwen2"
+    beside = {"dibizen": "kutirax", "gofezen": "dibizen"}.get(args.design, "qwen2")
     result = {"design": args.design.capitalize(), "beside": beside.capitalize(), "sizes": args.design_sizes, "width": z["width"], "layers": 4,
               "dtype": "bfloat16", "data": "synthetic", "prefill_tokens": args.prefill_tokens, "points": {}}
     sampler = ClockSampler()
@@ -879,8 +900,8 @@ def main() -> int:
                     help="profiling aid with --only decode_b<batch>: prompts of this many tokens instead of 512")
     ap.add_argument("--no-skip", action="store_true", help="profiling aid: time the decode steps right behind the prompt")
     ap.add_argument("--no-fp32", action="store_true", help="leave out the float32 engine's points")
-    ap.add_argument("--design", default="", choices=["", "kutirax", "bobunex", "dibizen"],
-                    help="measure another design beside Qwen2 (Dibizen: beside Kutirax) at equal width and depth instead of the "
+    ap.add_argument("--design", default="", choices=["", "kutirax", "bobunex", "dibizen", "gofezen"],
+                    help="measure another design beside Qwen2 (Dibizen: beside Kutirax; Gofezen: beside Dibizen) at equal width and depth instead of the "
                          "headline bench")
     ap.add_argument("--design-sizes", default="s", choices=sorted(DESIGN_SIZES), help="with --design: which layer sizes")
     ap.add_argument("--kernels", action="store_true", help="with --design: add device time by kernel name (profiler)")

@@ -276,8 +276,8 @@ template <typename T>
 __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ den,
                                                              const float* __restrict__ gate,
                                                              long long gate_stride, int gate_act, const float* __restrict__ w,
-                                                             float eps, T* __restrict__ out, int heads, int dv,
-                                                             long long n_pairs) {
+                                                             float eps, T* __restrict__ out, long long out_ld, int heads,
+                                                             int dv, long long n_pairs) {
   pdl_launch_dependents();
   pdl_wait();
   const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -295,7 +295,7 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __rest
   const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
   for (int i = lane; i < dv; i += 32) {
     const int c = hd * dv + i;
-    out[(size_t)pair * dv + i] = from_float<T>(src[i] / dn * rstd * w[c] * gate_value(gate, (size_t)t * gate_stride + c, gate_act));
+    out[(size_t)t * out_ld + c] = from_float<T>(src[i] / dn * rstd * w[c] * gate_value(gate, (size_t)t * gate_stride + c, gate_act));
   }
 }
 
@@ -304,7 +304,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) head_norm_gate_block_kernel(const float* __restrict__ y, const float* __restrict__ den,
                                                                    const float* __restrict__ gate, long long gate_stride,
                                                                    int gate_act, const float* __restrict__ w, float eps,
-                                                                   T* __restrict__ out, int heads, int dv) {
+                                                                   T* __restrict__ out, long long out_ld, int heads, int dv) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(256) head_norm_gate_block_kernel(const float* 
   }
   const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)dv + eps);
   for (int i = threadIdx.x; i < dv; i += blockDim.x)
-    out[(size_t)pair * dv + i] = from_float<T>(src[i] / dn * rstd * w[hd * dv + i] * gate_value(gate, g0 + i, gate_act));
+    out[(size_t)t * out_ld + (size_t)hd * dv + i] = from_float<T>(src[i] / dn * rstd * w[hd * dv + i] * gate_value(gate, g0 + i, gate_act));
 }
 
 }  // namespace tmk
@@ -404,17 +404,18 @@ extern "C" int tm_weighted_pair(int dtype, const void* a, const void* b, float s
 }
 
 // y [T, heads * dv] float; den [T, heads] float or null; gate: float pre-activations, element (t, c) at
-// gate + t * gate_stride + c, through a sigmoid (gate_act 0) or silu (1), or null for no gate; w [heads * dv].
+// gate + t * gate_stride + c, through a sigmoid (gate_act 0) or silu (1), or null for no gate; w [heads * dv]; out:
+// element (t, c) at out + t * out_ld + c.
 extern "C" int tm_head_norm_gate(int dtype, const float* y, const float* den, const float* gate, long long gate_stride,
-                                 int gate_act, const float* w, float eps, void* out, int T_rows, int heads, int dv,
-                                 cudaStream_t stream) {
+                                 int gate_act, const float* w, float eps, void* out, long long out_ld, int T_rows, int heads,
+                                 int dv, cudaStream_t stream) {
   if (T_rows <= 0) return 0;
   if (gate_act != 0 && gate_act != 1) return TM_ERR_UNSUPPORTED_SHAPE;
   const long long pairs = (long long)T_rows * heads;
   if (dv >= 512) {
     TM_BY_DTYPE(dtype, return launch_pdl(head_norm_gate_block_kernel<T>, dim3((unsigned)pairs), dim3(256), 0, stream, y, den, gate,
-                                         gate_stride, gate_act, w, eps, (T*)out, heads, dv))
+                                         gate_stride, gate_act, w, eps, (T*)out, out_ld, heads, dv))
   }
   TM_BY_DTYPE(dtype, return launch_pdl(head_norm_gate_kernel<T>, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, stream, y,
-                                       den, gate, gate_stride, gate_act, w, eps, (T*)out, heads, dv, pairs))
+                                       den, gate, gate_stride, gate_act, w, eps, (T*)out, out_ld, heads, dv, pairs))
 }

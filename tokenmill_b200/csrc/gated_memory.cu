@@ -64,12 +64,22 @@ __device__ __forceinline__ void gm_cp16(float* dst, const float* src) {
 }
 __device__ __forceinline__ void gm_cp_wait() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
+// W consecutive elements per access (W = 4: 16 bytes of float, 8 of bfloat16; the pointer must be aligned so).
+template <int W, typename T> __device__ __forceinline__ void ldw(const T* p, float (&v)[W]) {
+  if constexpr (W == 4) load4(p, v);
+  else v[0] = to_float(p[0]);
+}
+template <int W, typename T> __device__ __forceinline__ void stw(T* p, const float (&v)[W]) {
+  if constexpr (W == 4) store4(p, v);
+  else p[0] = from_float<T>(v[0]);
+}
+
 __device__ __forceinline__ float gm_softplus(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 __device__ __forceinline__ float gm_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // vec: bit 0 = the q and k columns, bit 1 = the v columns may be copied 16 bytes at a time.
 template <int MODE, bool ROWDECAY, bool DELTA>
-__global__ void __launch_bounds__(kGmThreads, 2) gated_memory_kernel(
+__global__ void __launch_bounds__(kGmThreads, 4) gated_memory_kernel(
     const float* __restrict__ proj, long long ld, int q_col, int k_col, int v_col, int vec, const float* __restrict__ gb,
     float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ cu_q,
     const int* __restrict__ state_slots, float* __restrict__ y, int heads, int qk_heads, int d, int dv, int parts, int cols,
@@ -127,6 +137,11 @@ __global__ void __launch_bounds__(kGmThreads, 2) gated_memory_kernel(
 
   const int n_chunks = (n_tok + chunk - 1) / chunk;
   const int v_live = max(0, min(cols, dv - tile * cols));
+  float row_live[ROWDECAY ? R : 1];                       // 1 for the rows that exist: the key 1 - f is 0 on the padding
+  if (ROWDECAY) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) row_live[r] = (r >> 2) * gs + part * 4 + (r & 3) < d ? 1.f : 0.f;
+  }
 
   auto stage = [&](int ci) {                               // asynchronous copies of chunk ci into its buffer
     float* buf = smem + (ci & 1) * buf_floats;
@@ -194,16 +209,11 @@ __global__ void __launch_bounds__(kGmThreads, 2) gated_memory_kernel(
 #pragma unroll
         for (int r = 0; r < R; r += 4) {
           const float4 f4 = *reinterpret_cast<const float4*>(kr + (r >> 2) * gs);
-          // rows >= d: f reads 0, S stays 0 (v = 0 never holds there for a value column, so keep the key 0 too)
-          const int row0 = (r >> 2) * gs + part * 4;
-          k_reg[r] = row0 < d ? 1.0f - f4.x : 0.f;
-          k_reg[r + 1] = row0 + 1 < d ? 1.0f - f4.y : 0.f;
-          k_reg[r + 2] = row0 + 2 < d ? 1.0f - f4.z : 0.f;
-          k_reg[r + 3] = row0 + 3 < d ? 1.0f - f4.w : 0.f;
-          S[r] = fmaf(f4.x, S[r], k_reg[r] * v);
-          S[r + 1] = fmaf(f4.y, S[r + 1], k_reg[r + 1] * v);
-          S[r + 2] = fmaf(f4.z, S[r + 2], k_reg[r + 2] * v);
-          S[r + 3] = fmaf(f4.w, S[r + 3], k_reg[r + 3] * v);
+          // S <- f S + (1 - f) v = v + f (S - v) on the rows that exist; rows >= d read f = 0 and stay 0
+          S[r] = fmaf(f4.x, S[r] - v, v * row_live[r]);
+          S[r + 1] = fmaf(f4.y, S[r + 1] - v, v * row_live[r + 1]);
+          S[r + 2] = fmaf(f4.z, S[r + 2] - v, v * row_live[r + 2]);
+          S[r + 3] = fmaf(f4.w, S[r + 3] - v, v * row_live[r + 3]);
         }
       } else {
         const float g = gsm[tt];
@@ -212,8 +222,7 @@ __global__ void __launch_bounds__(kGmThreads, 2) gated_memory_kernel(
         for (int r = 0; r < R; r += 4) {
           const float4 k4 = *reinterpret_cast<const float4*>(kr + (r >> 2) * gs);
           k_reg[r] = k4.x, k_reg[r + 1] = k4.y, k_reg[r + 2] = k4.z, k_reg[r + 3] = k4.w;
-          if (DELTA) {
-            S[r] *= g, S[r + 1] *= g, S[r + 2] *= g, S[r + 3] *= g;
+          if (DELTA) {            // the sum down the column runs on the memory before its decay; g enters afterwards
             c0 = fmaf(S[r], k4.x, c0);
             c1 = fmaf(S[r + 1], k4.y, c1);
             c0 = fmaf(S[r + 2], k4.z, c0);
@@ -228,9 +237,9 @@ __global__ void __launch_bounds__(kGmThreads, 2) gated_memory_kernel(
         if (DELTA) {
           float c = c0 + c1;
           for (int off = parts >> 1; off > 0; off >>= 1) c += __shfl_xor_sync(0xffffffffu, c, off);
-          const float u = gsm[chunk + tt] * (v - c);
+          const float u = gsm[chunk + tt] * (v - g * c);
 #pragma unroll
-          for (int r = 0; r < R; ++r) S[r] = fmaf(k_reg[r], u, S[r]);
+          for (int r = 0; r < R; ++r) S[r] = fmaf(g, S[r], k_reg[r] * u);
         }
       }
       if (MODE != 1) {
@@ -258,21 +267,32 @@ __global__ void __launch_bounds__(kGmThreads, 2) gated_memory_kernel(
   }
 }
 
-// Between the two passes over time slices. One block per (tile of CT columns, head, request), a thread per row: slice
-// k's own memory in scratch becomes the memory at its start, S <- P S + own from slice to slice, and the slot receives
-// the memory after the last slice. Diagonal P: one number per row (column dv of the record). Full P (delta rule): column
-// dv + j of the record holds P[:, j]; the tile's columns of S go through shared memory so that every row reads them all.
+// Between the two passes over time slices. One block per (tile of CT columns, head, request): slice k's own memory in
+// scratch becomes the memory at its start, S <- P S + own from slice to slice, and the slot receives the memory after
+// the last slice. Diagonal P: one number per row (column dv of the record). Full P (delta rule): column dv + j of the
+// record holds P[:, j]; the tile's columns of S go through shared memory so that every row reads them all. Thread
+// (row r, share js): the sum over j is dealt out over JS threads a row, which meet in shared memory in the order of js.
 constexpr int kGmPassCols = 8;
+
+static_assert(kGmPassCols == 8, "a row of the tile is two 16-byte loads");
+// acc[c] += p * row[c] for the tile's eight columns; row lies in shared memory, 32-byte aligned.
+__device__ __forceinline__ void row_fma(float (&acc)[kGmPassCols], float p, const float* row) {
+  const float4 a = *reinterpret_cast<const float4*>(row), b = *reinterpret_cast<const float4*>(row + 4);
+  acc[0] = fmaf(p, a.x, acc[0]), acc[1] = fmaf(p, a.y, acc[1]), acc[2] = fmaf(p, a.z, acc[2]), acc[3] = fmaf(p, a.w, acc[3]);
+  acc[4] = fmaf(p, b.x, acc[4]), acc[5] = fmaf(p, b.y, acc[5]), acc[6] = fmaf(p, b.z, acc[6]), acc[7] = fmaf(p, b.w, acc[7]);
+}
 
 template <bool DELTA>
 __global__ void __launch_bounds__(512) gated_memory_pass_states_kernel(
     float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ cu_q,
     const int* __restrict__ state_slots, float* slice_S, int heads, int d, int dv, int d_pad, int slice_len, int max_slices,
-    int extra) {
-  extern __shared__ __align__(16) float cur_s[];           // [kGmPassCols][d_pad]
+    int extra, int JS) {
+  extern __shared__ __align__(16) float pass_s[];          // cur [d_pad][CT] (a row's CT numbers side by side), then partial sums [JS][CT][d_pad]
+  float* cur_s = pass_s;
+  float* part_s = pass_s + kGmPassCols * d_pad;
   pdl_launch_dependents();
   pdl_wait();
-  const int head = blockIdx.y, s = blockIdx.z, r = threadIdx.x;
+  const int head = blockIdx.y, s = blockIdx.z, r = threadIdx.x % d_pad, js = threadIdx.x / d_pad;
   const int q_len = cu_q[s + 1] - cu_q[s];
   if (q_len <= 0) return;
   const int c0 = blockIdx.x * kGmPassCols;
@@ -282,106 +302,199 @@ __global__ void __launch_bounds__(512) gated_memory_pass_states_kernel(
   float* slot = state + (size_t)state_slots[s] * state_stride + state_off + ((size_t)head * dv + c0) * d_pad + r;
   float cur[kGmPassCols];
 #pragma unroll
-  for (int c = 0; c < kGmPassCols; ++c) cur[c] = c < nc ? slot[(size_t)c * d_pad] : 0.f;
+  for (int c = 0; c < kGmPassCols; ++c) cur[c] = (c < nc && js == 0) ? slot[(size_t)c * d_pad] : 0.f;
+  const int j_per = (d + JS - 1) / JS;
+  const int j_lo = js * j_per, j_hi = min(d, j_lo + j_per);
+  // P does not depend on the chain: a slice's first kPre numbers of this thread's share of P[r, :] are loaded while the
+  // slice before it is multiplied, so that the chain waits for arithmetic only (shares of up to kPre numbers wholly).
+  constexpr int kPre = 32;
+  float p_next[kPre];
+  auto prefetch = [&](int k) {
+    const float* P = slice_S + ((size_t)s * max_slices + k) * per + ((size_t)head * (dv + extra) + dv) * d_pad + r;
+#pragma unroll
+    for (int u = 0; u < kPre; ++u) p_next[u] = j_lo + u < j_hi ? P[(size_t)(j_lo + u) * d_pad] : 0.f;
+  };
+  if (DELTA) prefetch(0);
   for (int k = 0; k < slices; ++k) {
     float* rec = slice_S + ((size_t)s * max_slices + k) * per + (size_t)head * (dv + extra) * d_pad;
     float* mine = rec + (size_t)c0 * d_pad + r;
     float own[kGmPassCols];
 #pragma unroll
-    for (int c = 0; c < kGmPassCols; ++c) own[c] = c < nc ? mine[(size_t)c * d_pad] : 0.f;
+    for (int c = 0; c < kGmPassCols; ++c) own[c] = (c < nc && js == 0) ? mine[(size_t)c * d_pad] : 0.f;
     if (DELTA) {
-      __syncthreads();
+      float p_cur[kPre];
 #pragma unroll
-      for (int c = 0; c < kGmPassCols; ++c) cur_s[c * d_pad + r] = cur[c];
+      for (int u = 0; u < kPre; ++u) p_cur[u] = p_next[u];
+      if (k + 1 < slices) prefetch(k + 1);
+      __syncthreads();
+      if (js == 0) {
+        *reinterpret_cast<float4*>(cur_s + r * kGmPassCols) = make_float4(cur[0], cur[1], cur[2], cur[3]);
+        *reinterpret_cast<float4*>(cur_s + r * kGmPassCols + 4) = make_float4(cur[4], cur[5], cur[6], cur[7]);
+      }
       __syncthreads();
       const float* P = rec + (size_t)dv * d_pad + r;         // P[r, j] at P[j * d_pad]
-      for (int j = 0; j < d; ++j) {
-        const float p = P[(size_t)j * d_pad];
+      float acc[kGmPassCols];
 #pragma unroll
-        for (int c = 0; c < kGmPassCols; ++c) own[c] = fmaf(p, cur_s[c * d_pad + j], own[c]);
+      for (int c = 0; c < kGmPassCols; ++c) acc[c] = 0.f;
+#pragma unroll
+      for (int u = 0; u < kPre; ++u) {
+        if (j_lo + u < j_hi) row_fma(acc, p_cur[u], cur_s + (j_lo + u) * kGmPassCols);
+      }
+      int j = j_lo + kPre;
+      for (; j + 8 <= j_hi; j += 8) {                        // the rest of a long share: eight loads in flight
+        float p[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) p[u] = P[(size_t)(j + u) * d_pad];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) row_fma(acc, p[u], cur_s + (j + u) * kGmPassCols);
+      }
+      for (; j < j_hi; ++j) {
+        row_fma(acc, P[(size_t)j * d_pad], cur_s + j * kGmPassCols);
+      }
+      if (JS > 1) {
+#pragma unroll
+        for (int c = 0; c < kGmPassCols; ++c) part_s[(js * kGmPassCols + c) * d_pad + r] = acc[c];
+        __syncthreads();
+        if (js == 0) {
+          for (int o = 0; o < JS; ++o)
+#pragma unroll
+            for (int c = 0; c < kGmPassCols; ++c) own[c] += part_s[(o * kGmPassCols + c) * d_pad + r];
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kGmPassCols; ++c) own[c] += acc[c];
       }
     } else {
       const float f = rec[(size_t)dv * d_pad + r];
 #pragma unroll
       for (int c = 0; c < kGmPassCols; ++c) own[c] = fmaf(f, cur[c], own[c]);
     }
+    if (js == 0) {
 #pragma unroll
-    for (int c = 0; c < kGmPassCols; ++c) {
-      if (c < nc) mine[(size_t)c * d_pad] = cur[c];
-      cur[c] = own[c];
+      for (int c = 0; c < kGmPassCols; ++c) {
+        if (c < nc) mine[(size_t)c * d_pad] = cur[c];
+        cur[c] = own[c];
+      }
     }
   }
+  if (js == 0) {
 #pragma unroll
-  for (int c = 0; c < kGmPassCols; ++c)
-    if (c < nc) slot[(size_t)c * d_pad] = cur[c];
+    for (int c = 0; c < kGmPassCols; ++c)
+      if (c < nc) slot[(size_t)c * d_pad] = cur[c];
+  }
 }
 
 // Thread (token, VEC channels). Only the thread of a request's first row touches the slot: it computes the up to
-// taps - 1 outputs that need carried inputs, then writes the step's last taps - 1 inputs back.
-template <int VEC>
+// taps - 1 outputs that need carried inputs, then writes the step's last taps - 1 inputs back. TAPS: the number of taps
+// when it is 1 to 5 (loops unrolled, everything in registers), 0 for any number up to kGmMaxTaps.
+template <int VEC, int TAPS>
 __global__ void __launch_bounds__(128) short_conv_state_kernel(
-    const float* __restrict__ proj, long long ld, int col0, int channels, int taps, const float* __restrict__ weight,
+    const float* __restrict__ proj, long long ld, int col0, int channels, int taps_rt, const float* __restrict__ weight,
     const float* __restrict__ bias, float* __restrict__ state, long long state_stride, long long state_off,
     const int* __restrict__ cu_q, const int* __restrict__ seq_of_token, const int* __restrict__ state_slots, int act,
     float* __restrict__ out, long long out_ld, int out_col0) {
+  constexpr int NT = TAPS ? TAPS : kGmMaxTaps;
+  const int taps = TAPS ? TAPS : taps_rt;
   pdl_launch_dependents();
-  pdl_wait();
   const int t = blockIdx.x;
   const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
-  if (c0 >= channels) return;
+  if (c0 >= channels) {
+    pdl_wait();
+    return;
+  }
+  float w[VEC][NT], bv[VEC];                 // (weights: before the wait)
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    bv[e] = bias ? bias[c0 + e] : 0.f;
+#pragma unroll
+    for (int k = 0; k < NT; ++k) w[e][k] = k < taps ? weight[(size_t)(c0 + e) * taps + k] : 0.f;
+  }
+  pdl_wait();
   const int s = seq_of_token[t];
   const int first = cu_q[s];
   const int j = t - first;
   const int carried = taps - 1;
   if (j > 0 && j < carried) return;          // the first row's thread computes these
-  if (j >= carried) {
-    float acc[VEC], bv[VEC];
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      acc[e] = 0.f;
-      bv[e] = bias ? bias[c0 + e] : 0.f;
+  auto load = [&](int row, float (&u)[VEC]) {
+    const float* src = proj + (size_t)row * ld + col0 + c0;
+    if constexpr (VEC == 4) {
+      const float4 x = *reinterpret_cast<const float4*>(src);
+      u[0] = x.x + bv[0], u[1] = x.y + bv[1], u[2] = x.z + bv[2], u[3] = x.w + bv[3];
+    } else {
+      u[0] = src[0] + bv[0];
     }
-    for (int k = 0; k < taps; ++k) {
-      const float* src = proj + (size_t)(t - carried + k) * ld + col0 + c0;
-      float u[VEC];
-      if (VEC == 4) {
-        const float4 x = *reinterpret_cast<const float4*>(src);
-        u[0] = x.x, u[1] = x.y, u[2] = x.z, u[3] = x.w;
-      } else {
-        u[0] = src[0];
-      }
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(weight[(size_t)(c0 + e) * taps + k], u[e] + bv[e], acc[e]);
-    }
-    float* dst = out + (size_t)t * out_ld + out_col0 + c0;
+  };
+  auto store = [&](int row, const float (&acc)[VEC]) {
+    float* dst = out + (size_t)row * out_ld + out_col0 + c0;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) dst[e] = act ? acc[e] / (1.0f + expf(-acc[e])) : acc[e];
+  };
+  if (j >= carried) {
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int k = 0; k < NT; ++k) {
+      if (k >= taps) break;
+      float u[VEC];
+      load(t - carried + k, u);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(w[e][k], u[e], acc[e]);
+    }
+    store(t, acc);
     return;
   }
-  // j == 0: this thread owns the request's carried inputs of its channels.
+  // j == 0: this thread owns the request's carried inputs of its channels. win[i] for i < carried: the inputs before
+  // the step, oldest first; from there on the step's own rows.
   const int q_len = cu_q[s + 1] - first;
-  for (int e = 0; e < VEC; ++e) {
-    const int c = c0 + e;
-    float w[kGmMaxTaps], old[kGmMaxTaps];
-    for (int k = 0; k < taps; ++k) w[k] = weight[(size_t)c * taps + k];
-    const float bv = bias ? bias[c] : 0.f;
-    const float* in = proj + col0 + c;
-    float* slot = state + (size_t)state_slots[s] * state_stride + state_off + c;     // carried input i at slot[i * channels]
-    for (int i = 0; i < carried; ++i) old[i] = slot[(size_t)i * channels];
-    const int n_head = min(max(carried, 1), q_len);
-    for (int jj = 0; jj < n_head; ++jj) {
-      float acc = 0.f;
-      for (int k = 0; k < taps; ++k) {
-        const int src = jj - carried + k;        // offset inside the step; negative: carried input carried + src
-        const float v = src >= 0 ? in[(size_t)(first + src) * ld] + bv : old[carried + src];
-        acc = fmaf(w[k], v, acc);
-      }
-      out[(size_t)(first + jj) * out_ld + out_col0 + c] = act ? acc / (1.0f + expf(-acc)) : acc;
+  float* slot = state + (size_t)state_slots[s] * state_stride + state_off + c0;     // carried input i at slot[i * channels]
+  float win[2 * NT][VEC];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    if (i >= carried) break;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) win[i][e] = slot[(size_t)i * channels + e];
+  }
+  const int n_head = min(max(carried, 1), q_len);        // rows this thread computes (one tap: the row itself)
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    if (i >= n_head) break;
+    load(first + i, win[NT == kGmMaxTaps ? carried + i : TAPS - 1 + i]);
+  }
+#pragma unroll
+  for (int jj = 0; jj < NT; ++jj) {
+    if (jj >= n_head) break;
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int k = 0; k < NT; ++k) {
+      if (k >= taps) break;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(w[e][k], win[jj + k][e], acc[e]);
     }
-    for (int i = 0; i < carried; ++i) {
-      const int src = q_len - carried + i;
-      slot[(size_t)i * channels] = src >= 0 ? in[(size_t)(first + src) * ld] + bv : old[i + q_len];
+    store(first + jj, acc);
+  }
+  // the step's last `carried` inputs: row q_len - carried + i of the step, or what was carried when the step is shorter
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    if (i >= carried) break;
+    const int src = q_len - carried + i;
+    float u[VEC];
+    if (src >= n_head) {
+      load(first + src, u);
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) u[e] = 0.f;
+#pragma unroll
+      for (int m = 0; m < 2 * NT; ++m)                   // win[carried + src], picked without indexing the registers
+        if (m == carried + src) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) u[e] = win[m][e];
+        }
     }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) slot[(size_t)i * channels + e] = u[e];
   }
 }
 
@@ -428,20 +541,46 @@ __global__ void __launch_bounds__(256) forget_gate_prepare_kernel(float* __restr
 }
 
 // o [T, H, G, dv] float: head g's softmax weights applied to the values of every key/value head. out[t, h, :] =
-// sum_g talk[h, g] o[t, g, h / (H / G), :]. One block per token.
-template <typename T>
+// scale * sum_g talk[h, g] o[t, g, h / (H / G), :]. One block per token, a thread per four neighbouring numbers of the
+// output where dv allows; talk lies in shared memory and four heads' loads are in flight at a time.
+template <typename T, int W>
 __global__ void __launch_bounds__(256) talk_mix_kernel(const float* __restrict__ o, const float* __restrict__ talk,
-                                                       T* __restrict__ out, int H, int G, int dv) {
+                                                       T* __restrict__ out, int H, int G, int dv, float scale,
+                                                       long long out_ld) {
+  extern __shared__ float talk_s[];
   pdl_launch_dependents();
+  for (int i = threadIdx.x; i < H * H; i += blockDim.x) talk_s[i] = talk[i];      // (weights: before the wait)
   pdl_wait();
+  __syncthreads();
   const size_t t = blockIdx.x;
   const int Gq = H / G;
-  for (int idx = threadIdx.x; idx < H * dv; idx += blockDim.x) {
+  for (int idx = threadIdx.x * W; idx < H * dv; idx += blockDim.x * W) {
     const int h = idx / dv, e = idx - h * dv;
     const int c = h / Gq;
-    float acc = 0.f;
-    for (int g = 0; g < H; ++g) acc = fmaf(talk[h * H + g], o[((t * H + g) * G + c) * dv + e], acc);
-    out[t * H * dv + idx] = from_float<T>(acc);
+    const float* src = o + ((t * H) * G + c) * dv + e;       // head g's at src + g * G * dv
+    const float* tw = talk_s + h * H;
+    float acc[W];
+#pragma unroll
+    for (int i = 0; i < W; ++i) acc[i] = 0.f;
+    int g = 0;
+    for (; g + 4 <= H; g += 4) {
+      float x[4][W];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) ldw<W>(src + (size_t)(g + u) * G * dv, x[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int i = 0; i < W; ++i) acc[i] = fmaf(tw[g + u], x[u][i], acc[i]);
+    }
+    for (; g < H; ++g) {
+      float x[W];
+      ldw<W>(src + (size_t)g * G * dv, x);
+#pragma unroll
+      for (int i = 0; i < W; ++i) acc[i] = fmaf(tw[g], x[i], acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < W; ++i) acc[i] *= scale;
+    stw<W>(out + t * out_ld + idx, acc);
   }
 }
 
@@ -502,12 +641,19 @@ extern "C" int tm_gated_memory_pass_states(float* state, long long state_stride,
     return TM_ERR_UNSUPPORTED_SHAPE;
   const GmGeometry g = gm_geometry(d);
   const dim3 grid((dv + kGmPassCols - 1) / kGmPassCols, heads, n_seqs);
-  const size_t smem = sizeof(float) * kGmPassCols * g.d_pad;
-  if (delta)
-    return launch_pdl(gated_memory_pass_states_kernel<true>, grid, dim3(g.d_pad), smem, stream, state, state_stride, state_off,
-                      cu_q, state_slots, slice_S, heads, d, dv, g.d_pad, slice_len, max_slices, d);
-  return launch_pdl(gated_memory_pass_states_kernel<false>, grid, dim3(g.d_pad), smem, stream, state, state_stride, state_off,
-                    cu_q, state_slots, slice_S, heads, d, dv, g.d_pad, slice_len, max_slices, 1);
+  if (delta) {
+    const int JS = 512 / g.d_pad;         // threads that share a row's sum over j (1 for memories of 512 rows)
+    const size_t smem = sizeof(float) * kGmPassCols * g.d_pad * (1 + (JS > 1 ? JS : 0));
+    auto kern = gated_memory_pass_states_kernel<true>;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    return launch_pdl(kern, grid, dim3(g.d_pad * JS), smem, stream, state, state_stride, state_off, cu_q, state_slots, slice_S,
+                      heads, d, dv, g.d_pad, slice_len, max_slices, d, JS);
+  }
+  return launch_pdl(gated_memory_pass_states_kernel<false>, grid, dim3(g.d_pad), 0, stream, state, state_stride, state_off,
+                    cu_q, state_slots, slice_S, heads, d, dv, g.d_pad, slice_len, max_slices, 1, 1);
 }
 
 // proj: float, element (t, c) of the input at proj + t * ld + col0 + c; weight [channels, taps] float (the last tap weighs
@@ -521,13 +667,29 @@ extern "C" int tm_short_conv_state(const float* proj, long long ld, int col0, in
   if (T_rows <= 0) return 0;
   if (taps < 1 || taps > kGmMaxTaps || channels < 1 || (act != 0 && act != 1)) return TM_ERR_UNSUPPORTED_SHAPE;
   const bool wide = !(channels & 3) && !(col0 & 3) && !(ld & 3) && !((uintptr_t)proj & 15);
-  if (wide)
-    return launch_pdl(short_conv_state_kernel<4>, dim3(T_rows, (channels / 4 + 127) / 128), dim3(128), 0, stream, proj, ld,
-                      col0, channels, taps, weight, bias, state, state_stride, state_off, cu_q, seq_of_token, state_slots, act,
-                      out, out_ld, out_col0);
-  return launch_pdl(short_conv_state_kernel<1>, dim3(T_rows, (channels + 127) / 128), dim3(128), 0, stream, proj, ld, col0,
-                    channels, taps, weight, bias, state, state_stride, state_off, cu_q, seq_of_token, state_slots, act, out,
-                    out_ld, out_col0);
+#define TM_CONV(VEC_, TAPS_)                                                                                                \
+  return launch_pdl(short_conv_state_kernel<VEC_, TAPS_>, dim3(T_rows, (channels / VEC_ + 127) / 128), dim3(128), 0, stream, \
+                    proj, ld, col0, channels, taps, weight, bias, state, state_stride, state_off, cu_q, seq_of_token,       \
+                    state_slots, act, out, out_ld, out_col0)
+  if (wide) {
+    switch (taps) {
+      case 1: TM_CONV(4, 1);
+      case 2: TM_CONV(4, 2);
+      case 3: TM_CONV(4, 3);
+      case 4: TM_CONV(4, 4);
+      case 5: TM_CONV(4, 5);
+      default: break;
+    }
+  }
+  switch (taps) {
+    case 1: TM_CONV(1, 1);
+    case 2: TM_CONV(1, 2);
+    case 3: TM_CONV(1, 3);
+    case 4: TM_CONV(1, 4);
+    case 5: TM_CONV(1, 5);
+    default: TM_CONV(1, 0);
+  }
+#undef TM_CONV
 }
 
 extern "C" int tm_delta_prepare(float* x, long long x_ld, int q_col, int k_col, int qk_heads, int d, float q_scale,
@@ -547,13 +709,23 @@ extern "C" int tm_forget_gate_prepare(float* x, long long ld, int q_col, int f_c
                     ld, q_col, f_col, n, low, bias);
 }
 
-extern "C" int tm_talk_mix(int dtype, const float* o, const float* talk, void* out, int T_rows, int H, int G, int dv,
-                           cudaStream_t stream) {
+// out: element (t, c) at out + t * out_ld + c, c < H dv (the heads may be columns of a wider matrix).
+extern "C" int tm_talk_mix(int dtype, const float* o, const float* talk, void* out, long long out_ld, float scale, int T_rows,
+                           int H, int G, int dv, cudaStream_t stream) {
   if (T_rows <= 0) return 0;
-  if (H < 1 || G < 1 || H % G || dv < 1) return TM_ERR_UNSUPPORTED_SHAPE;
-  if (dtype == TM_DTYPE_F32)
-    return launch_pdl(talk_mix_kernel<float>, dim3(T_rows), dim3(256), 0, stream, o, talk, (float*)out, H, G, dv);
-  if (dtype == TM_DTYPE_BF16)
-    return launch_pdl(talk_mix_kernel<__nv_bfloat16>, dim3(T_rows), dim3(256), 0, stream, o, talk, (__nv_bfloat16*)out, H, G, dv);
+  if (H < 1 || G < 1 || H % G || dv < 1 || H > 96) return TM_ERR_UNSUPPORTED_SHAPE;
+  const size_t smem = sizeof(float) * H * H;
+  const bool wide = !(dv & 3) && !(out_ld & 3) && !(((uintptr_t)o | (uintptr_t)out) & 15);
+#define TM_TALK(T_, W_)                                                                                              \
+  return launch_pdl(talk_mix_kernel<T_, W_>, dim3(T_rows), dim3(256), smem, stream, o, talk, (T_*)out, H, G, dv, scale, out_ld)
+  if (dtype == TM_DTYPE_F32) {
+    if (wide) TM_TALK(float, 4);
+    TM_TALK(float, 1);
+  }
+  if (dtype == TM_DTYPE_BF16) {
+    if (wide) TM_TALK(__nv_bfloat16, 4);
+    TM_TALK(__nv_bfloat16, 1);
+  }
+#undef TM_TALK
   return TM_ERR_BAD_DTYPE;
 }

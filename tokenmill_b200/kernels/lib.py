@@ -88,7 +88,7 @@ _SIGNATURES: dict[str, list] = {
     "tm_glu": [_I, _I, _P, _P, _I, _I, _P],
     "tm_norm_pair_mean": [_I, _P, _P, _P, _P, _F, _P, _I, _I, _P],
     "tm_weighted_pair": [_I, _P, _P, _F, _F, _P, _LL, _P],
-    "tm_head_norm_gate": [_I, _P, _P, _P, _LL, _I, _P, _F, _P, _I, _I, _I, _P],
+    "tm_head_norm_gate": [_I, _P, _P, _P, _LL, _I, _P, _F, _P, _LL, _I, _I, _I, _P],
     "tm_qk_norm_rope_write": [_I, _P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _F, _I, _I,
                               _I, _P, _P],
     "tm_sink_attention": [_I, _P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _P,
@@ -105,7 +105,7 @@ _SIGNATURES: dict[str, list] = {
     "tm_short_conv_state": [_P, _LL, _I, _I, _I, _P, _P, _P, _LL, _LL, _P, _P, _P, _I, _P, _LL, _I, _I, _P],
     "tm_delta_prepare": [_P, _LL, _I, _I, _I, _I, _F, _F, _P, _LL, _I, _I, _P, _P, _I, _P, _I, _P],
     "tm_forget_gate_prepare": [_P, _LL, _I, _I, _I, _P, _P, _I, _P],
-    "tm_talk_mix": [_I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tm_talk_mix": [_I, _P, _P, _P, _LL, _F, _I, _I, _I, _I, _P],
     "tm_selective_scan": [_I, _P, _I, _P, _LL, _I, _P, _LL, _I, _I, _P, _P, _P, _P, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I,
                           _P, _P, _P],
     "tm_selective_pass_states": [_I, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],

@@ -1198,15 +1198,15 @@ def head_norm_gate(y: torch.Tensor, gate: torch.Tensor | None, weight: torch.Ten
                    out: torch.Tensor, den: torch.Tensor | None = None, gate_act: str = "sigmoid") -> torch.Tensor:
     """y [T, heads * dv] float32 (divided by den [T, heads] first, where given): each head by its own root mean square,
     times weight [heads * dv], times sigmoid(gate) or silu(gate) (``gate_act``); gate [T, heads * dv] float32
-    pre-activations (rows may be strided), or None for no gate."""
+    pre-activations (rows may be strided), or None for no gate. out [T, heads * dv] may be columns of a wider matrix."""
     T, inner = y.shape
     if inner % heads or weight.numel() != inner or out.shape != y.shape or (den is not None and den.shape != (T, heads)) or \
-            gate_act not in HEAD_GATES or \
+            gate_act not in HEAD_GATES or out.stride(1) != 1 or not out.is_cuda or \
             (gate is not None and (gate.shape != y.shape or gate.stride(1) != 1 or gate.dtype != torch.float32)):
         raise lib.KernelError("head_norm_gate: shapes do not fit")
     lib.call("tm_head_norm_gate", _code(out.dtype), _req(y, "y", torch.float32), _opt(den, "den", torch.float32),
              gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0, HEAD_GATES[gate_act],
-             _req(weight, "weight", torch.float32), float(eps), _req(out, "out"), T, heads, inner // heads, _stream())
+             _req(weight, "weight", torch.float32), float(eps), out.data_ptr(), out.stride(0), T, heads, inner // heads, _stream())
     return out
 
 
@@ -1605,12 +1605,15 @@ def forget_gate_prepare(x: torch.Tensor, q_col: int, f_col: int, n: int, low: to
     return x
 
 
-def talk_mix(cross: torch.Tensor, talk: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, vdim: int) -> torch.Tensor:
+def talk_mix(cross: torch.Tensor, talk: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, vdim: int,
+             scale: float = 1.0) -> torch.Tensor:
     """cross [T, heads * kv_heads * vdim] float32 (head g's softmax weights applied to the values of every value head);
-    talk [heads, heads] float32; out [T, heads * vdim] <- sum_g talk[h, g] cross[t, g, value head of h]."""
+    talk [heads, heads] float32; out [T, heads * vdim] (rows may be strided: columns of a wider matrix) <- scale * sum_g
+    talk[h, g] cross[t, g, value head of h]."""
     T = cross.shape[0]
-    if cross.shape != (T, heads * kv_heads * vdim) or talk.shape != (heads, heads) or out.shape != (T, heads * vdim):
+    if cross.shape != (T, heads * kv_heads * vdim) or talk.shape != (heads, heads) or out.shape != (T, heads * vdim) or \
+            out.stride(1) != 1 or not out.is_cuda:
         raise lib.KernelError("talk_mix: shapes do not fit")
     lib.call("tm_talk_mix", _code(out.dtype), _req(cross, "cross", torch.float32), _req(talk, "talk", torch.float32),
-             _req(out, "out"), T, heads, kv_heads, vdim, _stream())
+             out.data_ptr(), out.stride(0), float(scale), T, heads, kv_heads, vdim, _stream())
     return out

@@ -75,6 +75,8 @@ class GatedDeltaMixer:
         self.carry = (self.taps - 1) * self.conv_width
         self.memory_off = -(-self.carry // 4) * 4             # the memories start on 16 bytes
         self.w_in = self.w_o = self.w_conv = self.w_norm = self.A_log = self.dt_bias = None
+        self._scales: set[float] = set()
+        self._scaled: dict[float, torch.Tensor] = {}
 
     def weight_specs(self) -> list[WeightSpec]:
         n, W, nh = self.names, self.hidden_size, self.nh
@@ -106,16 +108,41 @@ class GatedDeltaMixer:
         self.w_conv = torch.cat([tensors[n[f"{x}_conv"]] for x in "qkv"], dim=0).contiguous()
         self.w_o, self.A_log, self.dt_bias = tensors[n["o"]], tensors[n["A_log"]], tensors[n["dt_bias"]]
         self.w_norm = tensors[n["norm"]].repeat(self.nh).contiguous()       # the kernel reads one weight per output number
+        self._scaled = {s: (self.w_norm * s).contiguous() for s in self._scales}
 
     def projection_weight(self) -> torch.Tensor:
         """[proj_width, hidden] rows [q; k; v; beta; a; g]: what a shared product multiplies for this mixer."""
         return self.w_in
 
+    @property
+    def output_width(self) -> int:
+        return self.inner
+
+    def output_weight(self) -> torch.Tensor:
+        """[hidden, heads * vdim]: what multiplies the normed and gated heads (``forward_projected(heads_out=)`` leaves them)."""
+        return self.w_o
+
+    def use_output_scale(self, scale: float) -> None:
+        """Announce, before the weights are bound, a constant that ``forward_projected(out_scale=)`` will be called with:
+        the heads' norm weight times it is made when the weights are bound (never inside a step, which a graph may be
+        capturing)."""
+        self._scales.add(float(scale))
+
+    def _norm_weight(self, scale: float) -> torch.Tensor:
+        if scale == 1.0:
+            return self.w_norm
+        if scale not in self._scaled:
+            raise ValueError(f"output scale {scale} was not announced through use_output_scale before the weights were bound")
+        return self._scaled[scale]
+
     def forward(self, x: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
         return self.forward_projected(ops.linear32(x, self.w_in), step, cache)
 
-    def forward_projected(self, proj: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
-        """``proj`` [T, proj_width] float32 (a view of a wider product is fine)."""
+    def forward_projected(self, proj: torch.Tensor, step: StepInputs, cache: LayerCache, *,
+                          heads_out: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor | None:
+        """``proj`` [T, proj_width] float32 (a view of a wider product is fine). ``heads_out`` [T, heads * vdim] (columns of
+        a wider matrix): the normed and gated heads times ``out_scale`` are left there and the output product is the
+        caller's."""
         T, dev, c = proj.shape[0], proj.device, self.col
         off = cache.state_off
         qkv = torch.empty((T, self.conv_width), dtype=torch.float32, device=dev)
@@ -129,9 +156,10 @@ class GatedDeltaMixer:
                          state_off=off + self.memory_off, cu_q=step.cu_q, state_slots=step.state_slots, y=y,
                          n_seqs=step.n_seqs, heads=self.nh, qk_heads=self.nqk, dim=self.d, vdim=self.dv,
                          **_slices(step, self.nh, self.d, self.dv, True, "delta_slice_memories"))
-        gated = torch.empty((T, self.inner), dtype=self.dtype, device=dev)
-        ops.head_norm_gate(y, proj[:, c["g"]:c["g"] + self.inner], self.w_norm, self.eps, self.nh, gated, gate_act="silu")
-        return ops.linear(gated, self.w_o)
+        gated = heads_out if heads_out is not None else torch.empty((T, self.inner), dtype=self.dtype, device=dev)
+        ops.head_norm_gate(y, proj[:, c["g"]:c["g"] + self.inner], self._norm_weight(out_scale), self.eps, self.nh, gated,
+                           gate_act="silu")
+        return ops.linear(gated, self.w_o) if heads_out is None else None
 
 
 class ForgetGateMemoryMixer:

@@ -7,7 +7,11 @@ them keeps pages: the pair hands its ``LayerCache`` to both. Both may keep per-r
 holds the left one's floats followed by the right one's (padded to a multiple of four), and each side finds its share
 through ``LayerCache.state_off`` (a side that ignores the offset must be the only one with state, or the left). Mixers
 that can take their columns of a shared product (``projection_weight`` / ``forward_projected``) are fed from ONE matrix
-product over the concatenated weights, which keeps its 32-bit accumulator.
+product over the concatenated weights, which keeps its 32-bit accumulator. With ``combine="weighted"``, mixers that can
+leave what their output projection reads in columns of a shared matrix, times a constant (``output_width`` /
+``output_weight()`` / ``forward_projected(..., heads_out=, out_scale=)``), share ONE output product as well:
+``[left_scale * a | right_scale * b] [W_o,left | W_o,right]^T`` is the weighted sum, summed in the product's 32-bit
+accumulator.
 """
 
 from __future__ import annotations
@@ -41,6 +45,13 @@ class PairMixer:
         # where each side's state starts in a request's slot
         self.state_offs = (0, -(-needs[0].shape[0] // 4) * 4 if all(n is not None for n in needs) else 0)
         self.shared = all(callable(getattr(m, "forward_projected", None)) for m in self.sides)
+        self.joint_out = self.shared and combine == "weighted" and \
+            all(callable(getattr(m, "output_weight", None)) for m in self.sides)
+        self.w_o = None
+        if self.joint_out:
+            for m, s in zip(self.sides, self.scales):
+                if callable(getattr(m, "use_output_scale", None)):
+                    m.use_output_scale(s)
         self.w_out: list = [None, None]
         self.w_in = None
 
@@ -63,6 +74,8 @@ class PairMixer:
             self.w_out = [tensors[self.names["left_out"]], tensors[self.names["right_out"]]]
         if self.shared:
             self.w_in = torch.cat([m.projection_weight() for m in self.sides], dim=0).contiguous()
+        if self.joint_out:
+            self.w_o = torch.cat([m.output_weight() for m in self.sides], dim=1).contiguous()
 
     def cache_need(self):
         return next((n for n in (m.cache_need() for m in self.sides) if n is not None), None)
@@ -80,6 +93,13 @@ class PairMixer:
     def forward(self, x: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
         caches = [cache if off == cache.state_off else dataclasses.replace(cache, state_off=cache.state_off + off)
                   for off in self.state_offs]
+        if self.joint_out:
+            proj = ops.linear32(x, self.w_in)
+            split, wide = self.sides[0].proj_width, self.sides[0].output_width
+            heads = torch.empty((x.shape[0], wide + self.sides[1].output_width), dtype=self.dtype, device=x.device)
+            self.sides[0].forward_projected(proj[:, :split], step, caches[0], heads_out=heads[:, :wide], out_scale=self.scales[0])
+            self.sides[1].forward_projected(proj[:, split:], step, caches[1], heads_out=heads[:, wide:], out_scale=self.scales[1])
+            return ops.linear(heads, self.w_o)
         if self.shared:
             proj = ops.linear32(x, self.w_in)
             split = self.sides[0].proj_width

@@ -212,6 +212,9 @@ class InputScaledExperts:
         n = self.names
         # the router's rows, then the shared expert's gate as one more row: one 32-bit product serves both
         rows = [tensors[n["router"]]] + ([tensors[n["shared_weight"]].reshape(1, -1)] if self.gated else [])
+        pad = -(self.E + len(rows) - 1) % 8          # rows of zeros up to a multiple of 8: the library's products of odd
+        if pad:                                       # widths run several times slower; nothing reads those columns
+            rows.append(torch.zeros((pad, self.hidden_size), dtype=rows[0].dtype, device=rows[0].device))
         self.w_router = torch.cat(rows, dim=0).contiguous()
         low = self.w_router.to(torch.bfloat16)
         self.w_router_low = low if self.dtype == torch.bfloat16 and bool((low.float() == self.w_router).all()) else None

@@ -166,6 +166,14 @@ class SinkWindowAttention:
         """[proj_width, hidden] rows [q; k; v; g]: what a shared product multiplies for this mixer."""
         return self.w_in
 
+    @property
+    def output_width(self) -> int:
+        return self.nh * self.dv
+
+    def output_weight(self) -> torch.Tensor:
+        """[hidden, heads * vdim]: what multiplies the heads side by side (``forward_projected(heads_out=)`` leaves them)."""
+        return self.w_o
+
     # --- per-step work list -----------------------------------------------------------------------------------
 
     def metadata_key(self):
@@ -194,9 +202,12 @@ class SinkWindowAttention:
     def forward(self, x: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
         return self.forward_projected(ops.linear32(x, self.w_in), step, cache)
 
-    def forward_projected(self, proj: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
+    def forward_projected(self, proj: torch.Tensor, step: StepInputs, cache: LayerCache, *,
+                          heads_out: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor | None:
         """``proj`` [T, proj_width] float32 (a view of a wider product is fine): this mixer's columns [q | k | v | g]
-        ([q | g] for a layer that reads another layer's keys and values)."""
+        ([q | g] for a layer that reads another layer's keys and values). ``heads_out`` [T, heads * vdim] (columns of a
+        wider matrix): the heads side by side times ``out_scale`` are left there and the output product is the caller's
+        (mixers with mixed heads, whose last kernel writes anywhere)."""
         T, dev = proj.shape[0], proj.device
         if self.taps or self.bias:      # q, k and v through the convolution (the biases enter on the way); what follows
             # reads that. Biases alone: a convolution of one tap with weights of one, which carries nothing.
@@ -215,20 +226,23 @@ class SinkWindowAttention:
                                cache=rows if cache.writes else None, gate_out=gate, has_kv=not self.shares_kv,
                                q_temp=self.q_temp, head_norm=self.head_norm)
         meta = step.meta[self.metadata_key()]
-        heads = torch.empty((T, self.nh * self.dv), dtype=self.dtype, device=dev)
+        if heads_out is not None and not self.talk:
+            raise NotImplementedError("only the mix of the heads writes into columns of a wider matrix")
+        heads = heads_out if heads_out is not None else torch.empty((T, self.nh * self.dv), dtype=self.dtype, device=dev)
         cross = torch.empty((T, self.nh * self.nkv * self.dv), dtype=torch.float32, device=dev) if self.talk else None
         splits, part = meta.host["n_splits"], None
         if splits > 1:
             part = step.workspace.get("sink_attention_part", meta.host["n_tiles"] * self.nkv * (self.nkv if self.talk else 1) *
                                       splits * self.tile_rows * (self.dv + 2), torch.float32)
         ops.sink_attention(q, cache.k, step.block_tables[cache.group], step.cu_q, step.kv_before, meta.arrays["tile_seq"],
-                           meta.arrays["tile_row0"], meta.host["n_tiles"], gate, heads, heads=self.nh, kv_heads=self.nkv,
+                           meta.arrays["tile_row0"], meta.host["n_tiles"], gate, None if self.talk else heads, heads=self.nh,
+                           kv_heads=self.nkv,
                            dim=self.d, vdim=self.dv, scale=self.scale, softcap=self.softcap, window=self.window,
                            keep_first=self.keep_first, sink=self.sink, tensor_cores=self.tensor_cores, n_splits=splits,
                            part=part, cross_out=cross)
         if self.talk:
-            ops.talk_mix(cross, self.w_talk, heads, self.nh, self.nkv, self.dv)
-        return ops.linear(heads, self.w_o)
+            ops.talk_mix(cross, self.w_talk, heads, self.nh, self.nkv, self.dv, scale=out_scale)
+        return ops.linear(heads, self.w_o) if heads_out is None else None
 
 
 register_mixer("sink_window_attention", SinkWindowAttention)
