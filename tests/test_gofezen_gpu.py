@@ -145,7 +145,7 @@ def _close(got, ref, dtype, what=""):
 
 # --- mechanisms alone -------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("channels,taps", [(72, 3), (100, 2), (33, 5), (40, 1), (8, 4)])
+@pytest.mark.parametrize("channels,taps", [(72, 3), (100, 2), (33, 5), (40, 1), (8, 4), (24, 7), (13, 16)])
 @pytest.mark.parametrize("bias,act", [(True, None), (False, "silu")])
 def test_short_convolution_carries_its_last_inputs(channels, taps, bias, act):
     """Two requests (slots 2 and 0 of 4) fed in steps of unequal sizes, single tokens and portions shorter than the
@@ -634,6 +634,30 @@ def test_layers_of_unlike_sizes(dtype, tmp_path):
     for mode in ("whole", "tail", "mixed"):
         steps, max_tokens = _steps(mode, reqs)
         _check(steps, run_trace(folder, dtype, steps, max_tokens, tmp_path / mode), reqs, plain, dtype)
+
+
+@pytest.mark.parametrize("kind", ["memories", "pairs"])
+def test_models_of_one_kind_of_layer(kind, tmp_path):
+    """Only forget-gate memories (no pages at all, one layer without a feed-forward) and only pairs (two page groups),
+    with seven taps on one side: mixed batches against the plain model."""
+    from tokenmill_b200.weights import write_random_model
+    from tokenmill_b200.weights.random_init import gofezen_config, gofezen_hgrn2 as R, gofezen_moe as E, gofezen_pair as P
+    if kind == "memories":
+        layers = [("hgrn2", R(heads=2, dim=20, vdim=12), E(experts=3, top=2, ff=16)), ("hgrn2", R(heads=4, dim=8, vdim=16), None),
+                  ("hgrn2", R(heads=1, dim=33, vdim=40), {"kind": "dense", "ff": 48})]
+    else:
+        layers = [("parallel", P(heads=2, kv_heads=1, dim=20, vdim=12, scale=0.3, conv=7, window=17, r_heads=2, r_qk_heads=1, r_dim=12,
+                                 r_vdim=20, r_conv=7), None),
+                  ("parallel", P(heads=3, kv_heads=3, dim=8, vdim=8, scale=0.4, conv=2, window=64, r_heads=4, r_qk_heads=4, r_dim=8,
+                                 r_vdim=10, r_conv=2, left_scale=0.7), E(experts=2, top=1, ff=24, shared=16))]
+    cfg = gofezen_config(vocab=131, width=40, max_positions=260, embedding_scale=5.0, logit_softcap=0.0, layers=layers)
+    folder = _lively(write_random_model(tmp_path / "m", cfg, seed=21))
+    _, w = _read(folder)
+    reqs = make_requests(131, [120, 75, 33, 90], seed=81)
+    plain = {r: _logits(cfg, w, t) for r, t in reqs.items()}
+    for mode in ("whole", "mixed"):
+        steps, max_tokens = _steps(mode, reqs)
+        check_against_plain(steps, run_trace(folder, "float32", steps, max_tokens, tmp_path / mode), reqs, plain, "float32")
 
 
 def test_slots_and_pages_used_again_start_clean(gofezen_dirs, plain_memo, tmp_path):
