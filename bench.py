@@ -730,7 +730,7 @@ DESIGN_SIZES = {
                            lightning=dict(heads=8, dim=128, vdim=128), mamba=dict(inner=2048, state=16, dt_rank=64, conv=4),
                            moe=dict(experts=14, top=2, ff=1024, identity=2, groups=(4, 2))),
               gofezen=dict(pair=dict(heads=8, kv_heads=2, dim=128, vdim=128, scale=128 ** -0.5, conv=3, window=512, r_heads=8,
-                                     r_qk_heads=4, r_dim=128, r_vdim=128, r_conv=4, left_scale=1.2, right_scale=1.1),
+                                     r_qk_heads=4, r_dim=128, r_vdim=128, r_conv=4, left_scale=0.9, right_scale=1.3),
                            hgrn2=dict(heads=8, dim=128, vdim=128), dense=2816, moe=dict(experts=14, top=2, ff=1024, shared=1024)),
               qwen=dict(num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=2816)),
     "m": dict(width=2048,
@@ -744,7 +744,7 @@ DESIGN_SIZES = {
                            lightning=dict(heads=16, dim=128, vdim=128), mamba=dict(inner=4096, state=16, dt_rank=128, conv=4),
                            moe=dict(experts=30, top=4, ff=1024, identity=2, groups=(8, 4))),
               gofezen=dict(pair=dict(heads=16, kv_heads=2, dim=128, vdim=128, scale=128 ** -0.5, conv=3, window=1024, r_heads=16,
-                                     r_qk_heads=8, r_dim=128, r_vdim=128, r_conv=4, left_scale=1.2, right_scale=1.1),
+                                     r_qk_heads=8, r_dim=128, r_vdim=128, r_conv=4, left_scale=0.9, right_scale=1.3),
                            hgrn2=dict(heads=16, dim=128, vdim=128), dense=5632, moe=dict(experts=30, top=4, ff=1024, shared=2048)),
               qwen=dict(num_attention_heads=16, num_key_value_heads=2, head_dim=128, intermediate_size=5632)),
 }
@@ -784,8 +784,8 @@ def design_model_dirs(size: str, vocab: int, design: str = "kutirax"):
             g = z["gofezen"]
             e, pair, mem = gofezen_moe(**g["moe"]), gofezen_pair(**g["pair"]), gofezen_hgrn2(**g["hgrn2"])
             beside_cfg = ("dibizen", kcfg)
-            kcfg = gofezen_config(vocab=vocab, width=z["width"], eps=1e-6, max_positions=4096, embedding_scale=z["width"] ** 0.5,
-                                  logit_scale=0.5, logit_softcap=30.0, layers=[
+            kcfg = gofezen_config(vocab=vocab, width=z["width"], eps=1e-6, max_positions=4096, embedding_scale=8.0,
+                                  logit_scale=0.7, logit_softcap=30.0, layers=[
                                       ("parallel", pair, {"kind": "dense", "ff": g["dense"]}), ("hgrn2", mem, e), ("hgrn2", mem, e),
                                       ("parallel", pair, e)])
     elif design == "bobunex":

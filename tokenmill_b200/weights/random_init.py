@@ -304,7 +304,7 @@ def _gofezen_named(name: str) -> dict | None:
             ("parallel", P(heads=3, kv_heads=1, dim=16, vdim=8, scale=0.25, conv=5, window=9, r_heads=5, r_qk_heads=5, r_dim=8,
                            r_vdim=8, r_conv=3, left_scale=2.0, right_scale=0.5), None)])
     if name == "gofezen-tiny-c":     # head sizes the tensor-core attention takes (bfloat16); wide memories
-        return gofezen_config(vocab=210, width=64, max_positions=350, embedding_scale=8.0, logit_scale=0.5, layers=[
+        return gofezen_config(vocab=210, width=64, max_positions=350, embedding_scale=8.0, logit_scale=0.6, layers=[
             ("parallel", P(heads=8, kv_heads=2, dim=64, vdim=32, scale=0.125, conv=4, window=70, r_heads=4, r_qk_heads=2, r_dim=64,
                            r_vdim=32, r_conv=4, left_scale=1.1, right_scale=0.9), E(experts=7, top=2, ff=16, shared=24)),
             ("hgrn2", R(heads=2, dim=70, vdim=16), E(experts=5, top=1, ff=24)),
