@@ -66,11 +66,12 @@ def windowed_attention_mixer(h, W, p, m, eps):
     proj = {}
     for name in ("q", "k", "v"):
         u = h @ W[p + name].T + W[p + name + ".b"]
-        proj[name] = causal_conv(u, W[p + name + ".conv"])
+        proj[name] = causal_conv(u, W[p + name + ".conv"]) if "conv" in m else u
     q = rms(proj["q"].view(T, H, d), eps)
     k = rms(proj["k"].view(T, G, d), eps)
     v = proj["v"].view(T, G, dv)
-    A = talking_heads(window_softmax_weights(q, k, m["scale"], m["mask"]["size"]), W[p + "talk"])
+    window = m["mask"]["size"] if m.get("mask") else T          # no mask: every earlier key
+    A = talking_heads(window_softmax_weights(q, k, m["scale"], window), W[p + "talk"])
     out = torch.zeros((T, H, dv), dtype=h.dtype)
     for hd in range(H):
         out[:, hd] = A[hd] @ v[:, hd // (H // G)]
@@ -100,9 +101,10 @@ def delta_rule(q, k, v, beta, g):
 def gated_delta_mixer(h, W, p, m, eps):
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = silu(causal_conv(h @ W[p + "q"].T, W[p + "q.conv"])).view(T, G, d)
-    k = silu(causal_conv(h @ W[p + "k"].T, W[p + "k.conv"])).view(T, G, d)
-    v = silu(causal_conv(h @ W[p + "v"].T, W[p + "v.conv"])).view(T, H, dv)
+    conv = (lambda u, name: causal_conv(u, W[p + name + ".conv"])) if "conv" in m else (lambda u, name: u)
+    q = silu(conv(h @ W[p + "q"].T, "q")).view(T, G, d)
+    k = silu(conv(h @ W[p + "k"].T, "k")).view(T, G, d)
+    v = silu(conv(h @ W[p + "v"].T, "v")).view(T, H, dv)
     q = unit(q) * d ** -0.5
     k = unit(k)
     rep = H // G

@@ -53,8 +53,8 @@ def test_config_reads_every_size_and_refuses_what_the_design_lacks():
                         (["layers", 1, "mlp", "ff"], 0), (["norm", "eps"], 0.0), (["logit_softcap"], -1.0), (["layers"], [])):
         with pytest.raises(ConfigError):
             GofezenConfig.from_dict(_set(raw, path, value))
-    for path in (["vocab"], ["norm"], ["max_positions"], ["layers", 0, "mixer", "left", "conv"],
-                 ["layers", 0, "mixer", "left", "mask"], ["layers", 1, "mixer", "vdim"], ["layers", 0, "mlp", "expert"]):
+    for path in (["vocab"], ["norm"], ["max_positions"], ["layers", 0, "mixer", "left", "scale"],
+                 ["layers", 0, "mixer", "right", "dim"], ["layers", 1, "mixer", "vdim"], ["layers", 0, "mlp", "expert"]):
         with pytest.raises(ConfigError):
             GofezenConfig.from_dict(_set(raw, path, delete=True))
 
@@ -62,9 +62,14 @@ def test_config_reads_every_size_and_refuses_what_the_design_lacks():
 def test_optional_keys_may_be_absent():
     raw = named_config("gofezen-tiny-a")
     for path in (["embedding"], ["logit_scale"], ["logit_softcap"], ["layers", 0, "mixer", "left_scale"],
-                 ["layers", 0, "mlp", "shared"]):
+                 ["layers", 0, "mlp", "shared"], ["layers", 3, "mixer", "left", "conv"], ["layers", 3, "mixer", "left", "mask"],
+                 ["layers", 0, "mixer", "right", "conv"]):
         raw = _set(raw, path, delete=True)
     cfg, model = _model(raw)
+    names = {w.name for w in model.weight_specs()}
+    assert not any(n.startswith("l3.mix.left.") and n.endswith(".conv") for n in names) and "l0.mix.left.q.conv" in names
+    assert "l0.mix.right.q.conv" not in names and "l3.mix.right.q.conv" in names
+    assert [g.need.window for g in model.cache_layout().groups] == [24, None]
     assert (cfg.embedding_scale, cfg.logit_scale, cfg.logit_softcap) == (1.0, 1.0, 0.0)
     spec = model.spec
     assert spec.layers[0].mixer.params["left_scale"] == 1.0 and spec.layers[0].mixer.params["right_scale"] == 0.8

@@ -639,7 +639,8 @@ def test_layers_of_unlike_sizes(dtype, tmp_path):
 @pytest.mark.parametrize("kind", ["memories", "pairs"])
 def test_models_of_one_kind_of_layer(kind, tmp_path):
     """Only forget-gate memories (no pages at all, one layer without a feed-forward) and only pairs (two page groups),
-    with seven taps on one side: mixed batches against the plain model."""
+    with seven taps in one layer, and in the other no mask (every earlier key) and no convolution on either side: mixed
+    batches against the plain model."""
     from tokenmill_b200.weights import write_random_model
     from tokenmill_b200.weights.random_init import gofezen_config, gofezen_hgrn2 as R, gofezen_moe as E, gofezen_pair as P
     if kind == "memories":
@@ -650,6 +651,7 @@ def test_models_of_one_kind_of_layer(kind, tmp_path):
                                  r_vdim=20, r_conv=7), None),
                   ("parallel", P(heads=3, kv_heads=3, dim=8, vdim=8, scale=0.4, conv=2, window=64, r_heads=4, r_qk_heads=4, r_dim=8,
                                  r_vdim=10, r_conv=2, left_scale=0.7), E(experts=2, top=1, ff=24, shared=16))]
+        del layers[1][1]["left"]["mask"], layers[1][1]["left"]["conv"], layers[1][1]["right"]["conv"]
     cfg = gofezen_config(vocab=131, width=40, max_positions=260, embedding_scale=5.0, logit_softcap=0.0, layers=layers)
     folder = _lively(write_random_model(tmp_path / "m", cfg, seed=21))
     _, w = _read(folder)

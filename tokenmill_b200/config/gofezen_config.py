@@ -11,6 +11,7 @@
     parallel mixer:   left  {heads, kv_heads, dim, vdim, scale, conv, mask.size}: windowed attention with biases, a short
                             convolution on q, k, v, a norm per head and mixed heads;
                       right {heads, kv_heads, dim, vdim, conv}: the gated delta rule (kv_heads counts its q/k heads);
+                      conv absent: no convolution and no tensors of it; mask absent: every earlier key is seen;
                       left_scale, right_scale: the weights of their sum (absent: 1)
     hgrn2 mixer:      heads, dim, vdim
 
@@ -62,17 +63,18 @@ class GofezenConfig:
                 _need(m, ("left", "right"), where + ".mixer")
                 _only(m, ("left", "right", "left_scale", "right_scale"), where + ".mixer")
                 a, r = m["left"], m["right"]
-                keys = ("heads", "kv_heads", "dim", "vdim", "scale", "conv", "mask")
+                keys = ("heads", "kv_heads", "dim", "vdim", "scale")
                 _need(a, keys, where + ".mixer.left")
-                _only(a, keys, where + ".mixer.left")
-                _need(a["mask"], ("size",), where + ".mixer.left.mask")
-                _only(a["mask"], ("size",), where + ".mixer.left.mask")
-                _pos_int(a["mask"]["size"], f"{where}.mixer.left.mask.size")
-                keys = ("heads", "kv_heads", "dim", "vdim", "conv")
+                _only(a, keys + ("conv", "mask"), where + ".mixer.left")
+                if a.get("mask") is not None:           # absent: every earlier key is seen
+                    _need(a["mask"], ("size",), where + ".mixer.left.mask")
+                    _only(a["mask"], ("size",), where + ".mixer.left.mask")
+                    _pos_int(a["mask"]["size"], f"{where}.mixer.left.mask.size")
+                keys = ("heads", "kv_heads", "dim", "vdim")
                 _need(r, keys, where + ".mixer.right")
-                _only(r, keys, where + ".mixer.right")
+                _only(r, keys + ("conv",), where + ".mixer.right")
                 for side, d in (("left", a), ("right", r)):
-                    for k in ("heads", "kv_heads", "dim", "vdim", "conv"):
+                    for k in ("heads", "kv_heads", "dim", "vdim") + (("conv",) if d.get("conv") is not None else ()):
                         _pos_int(d[k], f"{where}.mixer.{side}.{k}")
                     if d["heads"] % d["kv_heads"]:
                         raise ConfigError(f"config.json: {where}.mixer.{side}.heads must be a multiple of kv_heads")

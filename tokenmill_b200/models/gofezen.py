@@ -28,11 +28,12 @@ def gofezen_spec(cfg: GofezenConfig) -> ModelSpec:
             a, r = m["left"], m["right"]
             left = PartSpec("sink_window_attention", {
                 "hidden_size": d, "num_heads": a["heads"], "num_kv_heads": a["kv_heads"], "head_dim": a["dim"],
-                "value_dim": a["vdim"], "scale": float(a["scale"]), "position": None, "window": a["mask"]["size"],
+                "value_dim": a["vdim"], "scale": float(a["scale"]), "position": None,
+                "window": a["mask"]["size"] if a.get("mask") is not None else None,
                 "sink": False, "qk_norm": "head", "head_gate": False, "eps": cfg.eps, "bias": True,
-                "conv_taps": a["conv"], "talk": True})
+                "conv_taps": a.get("conv") or 0, "talk": True})
             right = PartSpec("gated_delta", {"hidden_size": d, "num_heads": r["heads"], "num_qk_heads": r["kv_heads"],
-                                             "head_dim": r["dim"], "value_dim": r["vdim"], "conv_taps": r["conv"],
+                                             "head_dim": r["dim"], "value_dim": r["vdim"], "conv_taps": r.get("conv") or 0,
                                              "eps": cfg.eps})
             mixer = PartSpec("pair", {"hidden_size": d, "eps": cfg.eps, "left": left, "right": right, "combine": "weighted",
                                       "left_scale": float(m.get("left_scale", 1.0)),

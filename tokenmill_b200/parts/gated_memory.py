@@ -58,11 +58,13 @@ class GatedDeltaMixer:
             raise ValueError(f"heads ({num_heads}) must be a multiple of q/k heads ({num_qk_heads})")
         if head_dim > 512:
             raise ValueError("memories of up to 512 rows per head are built")
-        if not 1 <= conv_taps <= 16:
-            raise ValueError(f"convolutions of 1 to 16 taps are built, got {conv_taps}")
+        if not 0 <= conv_taps <= 16:
+            raise ValueError(f"convolutions of up to 16 taps are built, got {conv_taps}")
         lib.prefer("delta")
         self.hidden_size, self.nh, self.nqk, self.d, self.dv = hidden_size, num_heads, num_qk_heads, head_dim, value_dim
-        self.taps, self.eps, self.unit_eps = int(conv_taps), float(eps), float(unit_eps)
+        # conv_taps 0: no convolution and no tensors of it (q, k, v go through silu alone)
+        self.has_conv, self.taps = conv_taps > 0, max(int(conv_taps), 1)
+        self.eps, self.unit_eps = float(eps), float(unit_eps)
         self.dtype, self.device = dtype, device
         self.names = {"q": "q", "k": "k", "v": "v", "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv", "beta": "b",
                       "a": "a", "A_log": "A_log", "dt_bias": "dt_bias", "g": "g", "norm": "norm", "o": "o", **(names or {})}
@@ -82,8 +84,9 @@ class GatedDeltaMixer:
         n, W, nh = self.names, self.hidden_size, self.nh
         specs = [WeightSpec(n["q"], (self.qk, W), init=("normal", 0.05)), WeightSpec(n["k"], (self.qk, W), init=("normal", 0.05)),
                  WeightSpec(n["v"], (self.inner, W), init=("normal", 0.05))]
-        specs += [WeightSpec(n[f"{x}_conv"], (size, self.taps), dtype="float32", init=("normal", 0.3, 1.0 / self.taps))
-                  for x, size in (("q", self.qk), ("k", self.qk), ("v", self.inner))]
+        if self.has_conv:
+            specs += [WeightSpec(n[f"{x}_conv"], (size, self.taps), dtype="float32", init=("normal", 0.3, 1.0 / self.taps))
+                      for x, size in (("q", self.qk), ("k", self.qk), ("v", self.inner))]
         specs += [WeightSpec(n["beta"], (nh, W), init=("normal", 0.05)), WeightSpec(n["a"], (nh, W), init=("normal", 0.05)),
                   WeightSpec(n["A_log"], (nh,), dtype="float32", init=("normal", 0.5, -1.0)),
                   WeightSpec(n["dt_bias"], (nh,), dtype="float32", init=("normal", 0.5)),
@@ -105,7 +108,10 @@ class GatedDeltaMixer:
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         n = self.names
         self.w_in = torch.cat([tensors[n[k]] for k in ("q", "k", "v", "beta", "a", "g")], dim=0).contiguous()
-        self.w_conv = torch.cat([tensors[n[f"{x}_conv"]] for x in "qkv"], dim=0).contiguous()
+        if self.has_conv:
+            self.w_conv = torch.cat([tensors[n[f"{x}_conv"]] for x in "qkv"], dim=0).contiguous()
+        else:       # one tap that weighs one: the kernel's activation alone
+            self.w_conv = torch.ones((self.conv_width, 1), dtype=torch.float32, device=self.device)
         self.w_o, self.A_log, self.dt_bias = tensors[n["o"]], tensors[n["A_log"]], tensors[n["dt_bias"]]
         self.w_norm = tensors[n["norm"]].repeat(self.nh).contiguous()       # the kernel reads one weight per output number
         self._scaled = {s: (self.w_norm * s).contiguous() for s in self._scales}
