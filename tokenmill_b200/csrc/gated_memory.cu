@@ -282,7 +282,9 @@ __device__ __forceinline__ void row_fma(float (&acc)[kGmPassCols], float p, cons
   acc[4] = fmaf(p, b.x, acc[4]), acc[5] = fmaf(p, b.y, acc[5]), acc[6] = fmaf(p, b.z, acc[6]), acc[7] = fmaf(p, b.w, acc[7]);
 }
 
-template <bool DELTA>
+// JP: a thread's share of the sum over j when every share has exactly that many numbers (d = JS * JP: no tests inside the
+// loops, the share's rows of P wholly prefetched); 0: any shape.
+template <bool DELTA, int JP>
 __global__ void __launch_bounds__(512) gated_memory_pass_states_kernel(
     float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ cu_q,
     const int* __restrict__ state_slots, float* slice_S, int heads, int d, int dv, int d_pad, int slice_len, int max_slices,
@@ -307,12 +309,16 @@ __global__ void __launch_bounds__(512) gated_memory_pass_states_kernel(
   const int j_lo = js * j_per, j_hi = min(d, j_lo + j_per);
   // P does not depend on the chain: a slice's first kPre numbers of this thread's share of P[r, :] are loaded while the
   // slice before it is multiplied, so that the chain waits for arithmetic only (shares of up to kPre numbers wholly).
-  constexpr int kPre = 32;
+  constexpr int kPre = JP ? JP : 32;
   float p_next[kPre];
   auto prefetch = [&](int k) {
-    const float* P = slice_S + ((size_t)s * max_slices + k) * per + ((size_t)head * (dv + extra) + dv) * d_pad + r;
+    const float* P = slice_S + ((size_t)s * max_slices + k) * per + ((size_t)head * (dv + extra) + dv + j_lo) * d_pad + r;
 #pragma unroll
-    for (int u = 0; u < kPre; ++u) p_next[u] = j_lo + u < j_hi ? P[(size_t)(j_lo + u) * d_pad] : 0.f;
+    for (int u = 0; u < kPre; ++u) {
+      if (JP || j_lo + u < j_hi) p_next[u] = *P;
+      else p_next[u] = 0.f;
+      P += d_pad;
+    }
   };
   if (DELTA) prefetch(0);
   for (int k = 0; k < slices; ++k) {
@@ -336,11 +342,12 @@ __global__ void __launch_bounds__(512) gated_memory_pass_states_kernel(
       float acc[kGmPassCols];
 #pragma unroll
       for (int c = 0; c < kGmPassCols; ++c) acc[c] = 0.f;
+      const float* rows = cur_s + j_lo * kGmPassCols;
 #pragma unroll
       for (int u = 0; u < kPre; ++u) {
-        if (j_lo + u < j_hi) row_fma(acc, p_cur[u], cur_s + (j_lo + u) * kGmPassCols);
+        if (JP || j_lo + u < j_hi) row_fma(acc, p_cur[u], rows + u * kGmPassCols);
       }
-      int j = j_lo + kPre;
+      int j = JP ? j_hi : j_lo + kPre;
       for (; j + 8 <= j_hi; j += 8) {                        // the rest of a long share: eight loads in flight
         float p[8];
 #pragma unroll
@@ -644,15 +651,22 @@ extern "C" int tm_gated_memory_pass_states(float* state, long long state_stride,
   if (delta) {
     const int JS = 512 / g.d_pad;         // threads that share a row's sum over j (1 for memories of 512 rows)
     const size_t smem = sizeof(float) * kGmPassCols * g.d_pad * (1 + (JS > 1 ? JS : 0));
-    auto kern = gated_memory_pass_states_kernel<true>;
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-    }
-    return launch_pdl(kern, grid, dim3(g.d_pad * JS), smem, stream, state, state_stride, state_off, cu_q, state_slots, slice_S,
-                      heads, d, dv, g.d_pad, slice_len, max_slices, d, JS);
+#define TM_GM_CHAIN(JP_)                                                                                                   \
+  {                                                                                                                        \
+    auto kern = gated_memory_pass_states_kernel<true, JP_>;                                                                \
+    if (smem > 48 * 1024) {                                                                                                \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                  \
+      if (e != cudaSuccess) return (int)e;                                                                                 \
+    }                                                                                                                      \
+    return launch_pdl(kern, grid, dim3(g.d_pad * JS), smem, stream, state, state_stride, state_off, cu_q, state_slots,     \
+                      slice_S, heads, d, dv, g.d_pad, slice_len, max_slices, d, JS);                                       \
   }
-  return launch_pdl(gated_memory_pass_states_kernel<false>, grid, dim3(g.d_pad), 0, stream, state, state_stride, state_off,
+    if (d == JS * 32) TM_GM_CHAIN(32)
+    if (d == JS * 8) TM_GM_CHAIN(8)
+    TM_GM_CHAIN(0)
+#undef TM_GM_CHAIN
+  }
+  return launch_pdl(gated_memory_pass_states_kernel<false, 0>, grid, dim3(g.d_pad), 0, stream, state, state_stride, state_off,
                     cu_q, state_slots, slice_S, heads, d, dv, g.d_pad, slice_len, max_slices, 1, 1);
 }
 
